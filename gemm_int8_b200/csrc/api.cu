@@ -1,0 +1,351 @@
+// C ABI of the library: argument validation, TMA descriptor construction, per-shape dispatch and
+// kernel launches.  No libtorch, no device allocation, no synchronisation on the compute path.
+#include "../../include/gemm_int8_b200.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "k_blockwise.cuh"
+#include "k_dense.cuh"
+
+namespace {
+
+using namespace gi8;
+
+constexpr int kMaxDevices = 64;
+constexpr int64_t kMaxK = 131072;  // |acc| <= 128*128*K must stay below 2^31 (no saturation modelled)
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...)
+{
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+#define GI8_CUDA(call)                                                                               \
+    do {                                                                                             \
+        cudaError_t e_ = (call);                                                                     \
+        if (e_ != cudaSuccess) return fail(GI8_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+// Kernel status word: one instance per device (module-scope device variable).
+__device__ uint32_t g_kernel_status;
+
+enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM };
+const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm"};
+int g_forced_variant = VAR_AUTO;
+
+struct DeviceState {
+    bool ready = false;
+    int sm_count = 0;
+    uint32_t* status = nullptr;
+    bool attr_set[32] = {};
+};
+
+std::mutex g_mutex;
+DeviceState g_dev[kMaxDevices];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int get_device_state(DeviceState** out)
+{
+    int dev = 0;
+    GI8_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(GI8_ERR_UNSUPPORTED_DEVICE, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState& st = g_dev[dev];
+    if (!st.ready) {
+        int major = 0, minor = 0;
+        GI8_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+        GI8_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
+        if (major != 10)
+            return fail(GI8_ERR_UNSUPPORTED_DEVICE, "device %d is sm_%d%d; this library is built for sm_100a only", dev,
+                        major, minor);
+        GI8_CUDA(cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev));
+        void* sym = nullptr;
+        GI8_CUDA(cudaGetSymbolAddress(&sym, g_kernel_status));
+        st.status = static_cast<uint32_t*>(sym);
+        if (!g_encode) {
+            void* fn = nullptr;
+            cudaDriverEntryPointQueryResult q;
+            GI8_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+            if (q != cudaDriverEntryPointSuccess || !fn)
+                return fail(GI8_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+            g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+        }
+        st.ready = true;
+    }
+    *out = &st;
+    return GI8_OK;
+}
+
+// Tensor map over a row-major int8 matrix [rows, K]: dimension 0 = K (contiguous), dimension 1 = rows.
+// Box = 128 bytes of K x box_rows rows, 128-byte swizzle, out-of-range elements read as zero.
+int make_operand_map(CUtensorMap* map, const int8_t* base, int64_t rows, int64_t K, int box_rows)
+{
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(GI8_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    return GI8_OK;
+}
+
+int check_common(const void* x, const void* y, const void* out, int64_t M, int64_t N, int64_t K, int out_align)
+{
+    if (M < 0 || N < 0 || K < 0) return fail(GI8_ERR_INVALID_ARGUMENT, "negative dimension (M=%lld N=%lld K=%lld)",
+                                             (long long)M, (long long)N, (long long)K);
+    if (M > INT32_MAX - 256 || N > INT32_MAX - 256)
+        return fail(GI8_ERR_UNSUPPORTED_SHAPE, "M and N must be below 2^31 - 256");
+    if (K >= kMaxK) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "K=%lld: K must be below %lld", (long long)K, (long long)kMaxK);
+    if (K % 16 != 0) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "K=%lld: K must be a multiple of 16", (long long)K);
+    if (M == 0 || N == 0) return GI8_OK;
+    if (!out) return fail(GI8_ERR_INVALID_ARGUMENT, "null output pointer");
+    if (reinterpret_cast<uintptr_t>(out) % out_align) return fail(GI8_ERR_MISALIGNED, "output pointer must be %d-byte aligned", out_align);
+    if (K == 0) return GI8_OK;
+    if (!x || !y) return fail(GI8_ERR_INVALID_ARGUMENT, "null operand pointer");
+    if (reinterpret_cast<uintptr_t>(x) % 16 || reinterpret_cast<uintptr_t>(y) % 16)
+        return fail(GI8_ERR_MISALIGNED, "x and y must be 16-byte aligned");
+    return GI8_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Dispatch: picks the tile width for the dense/blockwise kernels.  Model: the grid runs
+// ceil(tiles / SMs) waves; a wave of 128 x BN tiles costs about (BN + fixed overhead) per K block.
+// ---------------------------------------------------------------------------------------------------
+int pick_bn(int64_t M, int64_t N, int sms, bool allow64)
+{
+    const int cand[3] = {256, 128, 64};
+    int best = 256;
+    double best_cost = 1e300;
+    for (int i = 0; i < (allow64 ? 3 : 2); ++i) {
+        const int bn = cand[i];
+        const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+        const int64_t waves = (tiles + sms - 1) / sms;
+        const double cost = static_cast<double>(waves) * (bn + 24);
+        if (cost < best_cost) best_cost = cost, best = bn;
+    }
+    return best;
+}
+
+template <typename Kernel>
+int ensure_smem(DeviceState* st, int slot, Kernel kernel, size_t bytes)
+{
+    if (!st->attr_set[slot]) {
+        GI8_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
+        st->attr_set[slot] = true;
+    }
+    return GI8_OK;
+}
+
+template <int BN, int STAGES, int EPI>
+int launch_dense(DeviceState* st, int slot, const int8_t* x, const int8_t* y, DenseParams p, cudaStream_t stream)
+{
+    constexpr size_t smem = static_cast<size_t>(STAGES) * (kBM + BN) * kBK + 1024;
+    auto kernel = dense_gemm_kernel<BN, STAGES, EPI>;
+    if (int rc = ensure_smem(st, slot, kernel, smem)) return rc;
+    CUtensorMap mx, my;
+    if (int rc = make_operand_map(&mx, x, p.M, p.K, kBM)) return rc;
+    if (int rc = make_operand_map(&my, y, p.N, p.K, BN)) return rc;
+    p.tiles_m = (p.M + kBM - 1) / kBM;
+    p.tiles_n = (p.N + BN - 1) / BN;
+    const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+    const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+    kernel<<<grid, kDenseThreads, smem, stream>>>(mx, my, p);
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
+}
+
+template <int EPI>
+int dispatch_dense(DeviceState* st, const int8_t* x, const int8_t* y, DenseParams p, cudaStream_t stream)
+{
+    int bn;
+    switch (g_forced_variant) {
+        case VAR_DENSE_BN256: bn = 256; break;
+        case VAR_DENSE_BN128: bn = 128; break;
+        case VAR_DENSE_BN64: bn = 64; break;
+        default: bn = pick_bn(p.M, p.N, st->sm_count, true);
+    }
+    if (bn == 256) return launch_dense<256, 4, EPI>(st, EPI * 3 + 0, x, y, p, stream);
+    if (bn == 128) return launch_dense<128, 6, EPI>(st, EPI * 3 + 1, x, y, p, stream);
+    return launch_dense<64, 8, EPI>(st, EPI * 3 + 2, x, y, p, stream);
+}
+
+// K == 0: the product is all zeros; written with a plain memset-equivalent kernel.
+__global__ void fill_zero_kernel(uint8_t* out, int64_t bytes)
+{
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < bytes;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x)
+        out[i] = 0;
+}
+
+int zero_output(void* out, int64_t bytes, cudaStream_t stream)
+{
+    fill_zero_kernel<<<148, 256, 0, stream>>>(static_cast<uint8_t*>(out), bytes);
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int gi8_version(void) { return 100; }
+
+const char* gi8_last_error(void) { return g_err; }
+
+int gi8_force_variant(const char* name)
+{
+    if (!name || !*name) {
+        g_forced_variant = VAR_AUTO;
+        return GI8_OK;
+    }
+    for (int i = 0; i < 5; ++i)
+        if (!strcmp(name, kVariantNames[i])) {
+            g_forced_variant = i;
+            return GI8_OK;
+        }
+    return fail(GI8_ERR_INVALID_ARGUMENT, "unknown variant '%s'", name);
+}
+
+const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
+{
+    (void)K;
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
+    if (g_forced_variant != VAR_AUTO) return kVariantNames[g_forced_variant];
+    const int bn = pick_bn(M, N, sms, kind != 2);
+    return bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
+}
+
+int gi8_device_status(uint32_t* code)
+{
+    if (!code) return fail(GI8_ERR_INVALID_ARGUMENT, "null code pointer");
+    GI8_CUDA(cudaDeviceSynchronize());
+    uint32_t v = 0, zero = 0;
+    GI8_CUDA(cudaMemcpyFromSymbol(&v, g_kernel_status, sizeof(v)));
+    if (v) GI8_CUDA(cudaMemcpyToSymbol(g_kernel_status, &zero, sizeof(zero)));
+    *code = v;
+    return GI8_OK;
+}
+
+int gi8_matmul(const int8_t* x, const int8_t* y, void* out, int64_t M, int64_t N, int64_t K, float alpha, void* stream)
+{
+    if (int rc = check_common(x, y, out, M, N, K, 2)) return rc;
+    if (M == 0 || N == 0) return GI8_OK;
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 0) return zero_output(out, M * N * 2, s);
+    DenseParams p{};
+    p.out = out, p.status = st->status, p.ldo = N, p.M = (int)M, p.N = (int)N, p.K = (int)K, p.alpha = alpha;
+    p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
+    return dispatch_dense<EPI_ALPHA_BF16>(st, x, y, p, s);
+}
+
+int gi8_matmul_i32(const int8_t* x, const int8_t* y, int32_t* out, int64_t M, int64_t N, int64_t K, void* stream)
+{
+    if (int rc = check_common(x, y, out, M, N, K, 4)) return rc;
+    if (M == 0 || N == 0) return GI8_OK;
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 0) return zero_output(out, M * N * 4, s);
+    DenseParams p{};
+    p.out = out, p.status = st->status, p.ldo = N, p.M = (int)M, p.N = (int)N, p.K = (int)K, p.alpha = 1.0f;
+    p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 4 == 0);
+    return dispatch_dense<EPI_RAW_I32>(st, x, y, p, s);
+}
+
+int64_t gi8_matmul_scaled_workspace_bytes(int64_t M, int64_t N, int64_t K)
+{
+    (void)M, (void)N, (void)K;
+    return 0;
+}
+
+int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out, int64_t M,
+                      int64_t N, int64_t K, void* workspace, int64_t workspace_bytes, void* stream)
+{
+    (void)workspace, (void)workspace_bytes;
+    if (int rc = check_common(x, y, out, M, N, K, 2)) return rc;
+    if (M == 0 || N == 0) return GI8_OK;
+    if (!sx || !sw) return fail(GI8_ERR_INVALID_ARGUMENT, "null scale pointer");
+    if (reinterpret_cast<uintptr_t>(sx) % 4 || reinterpret_cast<uintptr_t>(sw) % 4)
+        return fail(GI8_ERR_MISALIGNED, "scale pointers must be 4-byte aligned");
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 0) return zero_output(out, M * N * 2, s);
+    DenseParams p{};
+    p.out = out, p.sx = sx, p.sw = sw, p.status = st->status, p.ldo = N, p.M = (int)M, p.N = (int)N, p.K = (int)K;
+    p.alpha = 1.0f;
+    p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
+    return dispatch_dense<EPI_ROWCOL_BF16>(st, x, y, p, s);
+}
+
+int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                         int64_t ld_sw, void* out, int64_t M, int64_t N, int64_t K, void* stream)
+{
+    if (int rc = check_common(x, y, out, M, N, K, 2)) return rc;
+    if (M == 0 || N == 0) return GI8_OK;
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 0) return zero_output(out, M * N * 2, s);
+    const int64_t KB = (K + kBK - 1) / kBK;
+    if (!sa || !sw) return fail(GI8_ERR_INVALID_ARGUMENT, "null scale pointer");
+    if (ld_sa < KB || ld_sw < KB)
+        return fail(GI8_ERR_INVALID_ARGUMENT, "scale row strides (%lld, %lld) must be at least ceil(K/128) = %lld",
+                    (long long)ld_sa, (long long)ld_sw, (long long)KB);
+    if (reinterpret_cast<uintptr_t>(sa) % 4 || reinterpret_cast<uintptr_t>(sw) % 4)
+        return fail(GI8_ERR_MISALIGNED, "scale pointers must be 4-byte aligned");
+    BlockwiseParams p{};
+    p.out = out, p.sa = sa, p.sw = sw, p.status = st->status, p.ldo = N, p.ld_sa = ld_sa, p.ld_sw = ld_sw;
+    p.M = (int)M, p.N = (int)N, p.K = (int)K;
+    p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
+    int bn;
+    switch (g_forced_variant) {
+        case VAR_DENSE_BN256: bn = 256; break;
+        case VAR_DENSE_BN128: bn = 128; break;
+        default: bn = pick_bn(M, N, st->sm_count, false);
+    }
+    CUtensorMap mx, my;
+    if (int rc = make_operand_map(&mx, x, M, K, kBM)) return rc;
+    p.tiles_m = (int)((M + kBM - 1) / kBM);
+    p.tiles_n = (int)((N + bn - 1) / bn);
+    const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+    const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+    if (bn == 256) {
+        constexpr size_t smem = 4 * (kBM + 256) * kBK + 1024;
+        auto kernel = blockwise_gemm_kernel<256, 4, CVT_MAGIC>;
+        if (int rc = ensure_smem(st, 16, kernel, smem)) return rc;
+        if (int rc = make_operand_map(&my, y, N, K, 256)) return rc;
+        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, p);
+    } else {
+        constexpr size_t smem = 6 * (kBM + 128) * kBK + 1024;
+        auto kernel = blockwise_gemm_kernel<128, 6, CVT_MAGIC>;
+        if (int rc = ensure_smem(st, 17, kernel, smem)) return rc;
+        if (int rc = make_operand_map(&my, y, N, K, 128)) return rc;
+        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, p);
+    }
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,108 @@
+/*
+ * C ABI of libgemm_int8_b200.so -- the B200 (sm_100a) INT8 GEMM library.
+ *
+ * This is the drop-in boundary for the reference project's native layer.  The reference binds its
+ * Python operator to C++ symbols that take torch::Tensor and are linked against libtorch
+ * (csrc/kernels/include/gemm.h:6-10, csrc/kernels/bindings.cpp:10-38).  Here the same work is exposed
+ * as plain C entry points: raw device pointers, sizes, a CUDA stream handle, an int status.  The caller
+ * owns every buffer (inputs, output, scratch); the library allocates no device memory, launches on the
+ * stream it is given and never synchronises, except where a function says otherwise.
+ *
+ * Conventions
+ *   x    int8  [M,K] row-major, contiguous         (reference operand A, bindings.cpp:10, gemm.cu:76-79)
+ *   y    int8  [N,K] row-major, contiguous         (reference operand B, "column-major K x N", gemm.cu:80-83)
+ *   out  bf16  [M,N] row-major, contiguous         (reference result C,  bindings.cpp:23, gemm.cu:85-88)
+ *   stream  a cudaStream_t passed as void* (NULL = the legacy default stream, which is what the
+ *           reference launches on, gemm.cu:118)
+ *   Requirements: x, y 16-byte aligned and K % 16 == 0 (the reference's CUTLASS alignment, which it
+ *   reports as "cutlass cannot implement", gemm.cu:107-110); out 2-byte aligned (16-byte aligned and
+ *   N % 8 == 0 selects vector stores; the reference requires N % 8 == 0).  M, N, K >= 0; K < 131072.
+ *   Every entry point returns GI8_OK or an error code; gi8_last_error() gives the message.
+ */
+#ifndef GEMM_INT8_B200_H_
+#define GEMM_INT8_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum gi8_status {
+    GI8_OK = 0,
+    GI8_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, bad leading dimension */
+    GI8_ERR_UNSUPPORTED_SHAPE = 2, /* K % 16 != 0, K too large, size beyond a stated limit */
+    GI8_ERR_MISALIGNED = 3,        /* a pointer violates the alignment stated above */
+    GI8_ERR_CUDA = 4,              /* a CUDA runtime/driver call failed (message has the detail) */
+    GI8_ERR_UNSUPPORTED_DEVICE = 5, /* the current device is not compute capability 10.0 */
+    GI8_ERR_WORKSPACE = 6,         /* scratch buffer missing or too small */
+    GI8_ERR_DEVICE_TIMEOUT = 7     /* a kernel reported a bounded wait that expired (gi8_device_status) */
+};
+
+/* Library version, major * 10000 + minor * 100 + patch. */
+int gi8_version(void);
+
+/* Message of the most recent failing call on the calling thread (never NULL). */
+const char* gi8_last_error(void);
+
+/*
+ * out = bf16( fp32(x @ y^T) * alpha ).
+ * Replaces int8_matmul_host / int8_matmul<Tile,Warp,Stages> (csrc/kernels/gemm.cu:22-162) as called
+ * from the torch op int8_matmul(Tensor A, Tensor B, float alpha) (csrc/kernels/bindings.cpp:10-26).
+ */
+int gi8_matmul(const int8_t* x, const int8_t* y, void* out_bf16, int64_t M, int64_t N, int64_t K, float alpha,
+               void* stream);
+
+/*
+ * acc = x @ y^T as raw int32 [M,N] (the accumulator the reference keeps in registers before its
+ * epilogue, csrc/kernels/gemm.cu:33-37).  For bit-exact verification; out_i32 must be 4-byte aligned.
+ */
+int gi8_matmul_i32(const int8_t* x, const int8_t* y, int32_t* out_i32, int64_t M, int64_t N, int64_t K,
+                   void* stream);
+
+/*
+ * out[m,n] = bf16( fp32(acc[m,n]) * (sx[m] * sw[n]) ), sx fp32 [M] per-token, sw fp32 [N] per output
+ * channel.  No counterpart in the reference (its epilogue takes one scalar, gemm.cu:96).
+ * Small-M shapes run a split-K weight-streaming kernel that needs scratch: `workspace` must hold at
+ * least gi8_matmul_scaled_workspace_bytes(M,N,K) bytes, 16-byte aligned, AND BE ZERO-FILLED before
+ * the first call; the kernel leaves it zero-filled again on completion, so one zeroed buffer can be
+ * reused by successive calls on the same stream.  Pass NULL/0 when that function returns 0.
+ */
+int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out_bf16,
+                      int64_t M, int64_t N, int64_t K, void* workspace, int64_t workspace_bytes, void* stream);
+
+int64_t gi8_matmul_scaled_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/*
+ * Blockwise-dequantised W8A8 GEMM:
+ *   out[m,n] = bf16( sum over kb (ascending) of  fp32(P[m,n,kb]) * (sa[m,kb] * sw[n/128,kb]) )
+ * accumulated with one fused multiply-add per K block; P is the exact int32 dot product over K block
+ * kb (128 wide).  sa fp32 [M, ceil(K/128)] with row stride ld_sa; sw fp32 [ceil(N/128), ceil(K/128)]
+ * with row stride ld_sw (strides in elements).  No counterpart in the reference.
+ */
+int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                         int64_t ld_sw, void* out_bf16, int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
+ * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted
+ * per-shape dispatch that replaces the reference's shape table (csrc/kernels/gemm.cu:136-161).
+ * Names: "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "auto".  Returns GI8_ERR_INVALID_ARGUMENT
+ * for an unknown name.
+ */
+int gi8_force_variant(const char* name);
+
+/* Name of the variant the dispatch would pick for (kind, M, N, K); kind: 0 plain, 1 scaled, 2 blockwise. */
+const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K);
+
+/*
+ * Reads and clears the current device's kernel status word.  SYNCHRONISES the device.  *code is 0 when
+ * every kernel since the last call ran to completion, else the first recorded failure
+ * (low byte: 1 producer, 2 MMA, 3 epilogue, 4 drain, 5 reduce wait expired; upper bits: CTA index).
+ */
+int gi8_device_status(uint32_t* code);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* GEMM_INT8_B200_H_ */

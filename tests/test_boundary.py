@@ -1,0 +1,106 @@
+"""CPU tests of the drop-in boundary: the C-ABI library loads and exports every declared symbol, the
+torch ops exist under the reference's names with working fake kernels, and argument validation that
+needs no GPU behaves as documented."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "gemm_int8_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(gi8_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from gemm_int8_b200 import _lib
+
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    names = _declared_symbols()
+    assert "gi8_matmul" in names and "gi8_matmul_blockwise" in names
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+    assert set(names) == set(_lib.SYMBOLS), "ctypes table and header disagree"
+
+
+def test_version_and_error_string():
+    import gemm_int8_b200 as g
+
+    assert g._C.gi8_version() >= 100
+    assert isinstance(g._C.gi8_last_error(), bytes)
+
+
+def test_host_side_validation_without_gpu():
+    """Shape/pointer checks run before any CUDA call, so they are testable on a CPU-only box."""
+    import gemm_int8_b200 as g
+
+    C = g._C
+    buf = ctypes.create_string_buffer(4096 + 64)
+    base = (ctypes.addressof(buf) + 63) & ~63
+    p = ctypes.c_void_p
+    assert C.gi8_matmul(p(base), p(base), p(base), -1, 8, 16, 1.0, None) == 1
+    assert C.gi8_matmul(p(base), p(base), p(base), 8, 8, 24, 1.0, None) == 2      # K % 16
+    assert b"multiple of 16" in C.gi8_last_error()
+    assert C.gi8_matmul(p(base), p(base), p(base), 8, 8, 131072, 1.0, None) == 2  # K limit
+    assert C.gi8_matmul(p(base + 1), p(base), p(base), 8, 8, 16, 1.0, None) == 3  # misaligned x
+    assert C.gi8_matmul(None, p(base), p(base), 8, 8, 16, 1.0, None) == 1
+    assert C.gi8_matmul(p(base), p(base), p(base + 1), 8, 8, 16, 1.0, None) == 3  # misaligned out
+    assert C.gi8_matmul(p(base), p(base), None, 0, 8, 16, 1.0, None) == 0         # empty problem is a no-op
+    assert C.gi8_matmul_i32(p(base), p(base), p(base + 2), 8, 8, 16, None) == 3
+    assert C.gi8_force_variant(b"nonsense") == 1
+    assert C.gi8_force_variant(b"dense_bn128") == 0 and C.gi8_force_variant(None) == 0
+
+
+def test_ops_registered_under_reference_names():
+    import gemm_int8  # noqa: F401  (the drop-in package name)
+
+    op = torch.ops.gemm_int8_CUDA.int8_matmul.default
+    assert str(op._schema) == "gemm_int8_CUDA::int8_matmul(Tensor A, Tensor B, float alpha) -> Tensor"
+    assert gemm_int8.__all__ == ["matmul"]
+    for name in ("int8_matmul_scaled", "int8_matmul_blockwise", "int8_matmul_i32"):
+        assert hasattr(torch.ops.gemm_int8_CUDA, name)
+
+
+def test_fake_kernels_propagate_shapes():
+    import gemm_int8
+    from torch._subclasses.fake_tensor import FakeTensorMode
+
+    with FakeTensorMode():
+        x = torch.empty(33, 256, dtype=torch.int8, device="cuda")
+        y = torch.empty(72, 256, dtype=torch.int8, device="cuda")
+        out = gemm_int8.matmul(x, y, 0.5)
+        assert out.shape == (33, 72) and out.dtype == torch.bfloat16 and out.device.type == "cuda"
+        sa = torch.empty(33, 2, dtype=torch.float32, device="cuda")
+        sw = torch.empty(1, 2, dtype=torch.float32, device="cuda")
+        assert gemm_int8.matmul_blockwise(x, y, sa, sw).shape == (33, 72)
+        sx = torch.empty(33, dtype=torch.float32, device="cuda")
+        sc = torch.empty(72, dtype=torch.float32, device="cuda")
+        assert gemm_int8.matmul_scaled(x, y, sx, sc).dtype == torch.bfloat16
+        with pytest.raises(Exception):
+            gemm_int8.matmul(x, torch.empty(72, 128, dtype=torch.int8, device="cuda"), 1.0)
+        with pytest.raises(Exception):
+            gemm_int8.matmul(x.to(torch.int32), y, 1.0)
+
+
+def test_cpu_tensors_are_rejected_not_computed():
+    """There is no CPU path: calling the op on CPU tensors must fail (the reference raises
+    NotImplementedError for the missing CPU kernel as well)."""
+    import gemm_int8
+
+    x = torch.zeros(8, 16, dtype=torch.int8)
+    with pytest.raises((NotImplementedError, RuntimeError)):
+        gemm_int8.matmul(x, x, 1.0)
+
+
+def test_product_does_not_import_oracle():
+    pkg = os.path.join(ROOT, "gemm_int8_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                text = open(os.path.join(dirpath, f)).read()
+                assert "oracle" not in text.replace("CPU oracle's blockwise restatement", ""), f
