@@ -7,11 +7,13 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
 #include "k_blockwise.cuh"
 #include "k_dense.cuh"
+#include "k_smallm.cuh"
 
 namespace {
 
@@ -201,6 +203,55 @@ int zero_output(void* out, int64_t bytes, cudaStream_t stream)
     return GI8_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Small-M plan: token tile MT, number of K splits and pipeline depth.  Two CTAs fit one SM (about 100 KB
+// of shared memory each), so the split count is chosen to fill 2 x SMs CTA slots without starting a
+// second partial wave, while every split keeps at least two K blocks.
+// ---------------------------------------------------------------------------------------------------
+struct SmallMPlan {
+    bool use;
+    int mt, splits, kb_per_split, tiles_n;
+    int64_t scratch_bytes, total_bytes;
+};
+
+constexpr int kSmallMMaxM = 64;  // the automatic dispatch sends M <= 64 to the small-M kernel
+
+SmallMPlan plan_smallm(int64_t M, int64_t N, int64_t K, int sms, bool forced)
+{
+    SmallMPlan pl{};
+    pl.use = (M >= 1) && (forced ? M <= 128 : M <= kSmallMMaxM) && K > 0 && N > 0;
+    if (!pl.use) return pl;
+    pl.mt = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    pl.tiles_n = static_cast<int>((N + kSmallMTileN - 1) / kSmallMTileN);
+    const int kb_total = static_cast<int>((K + kBK - 1) / kBK);
+    const int slots = 2 * sms;
+    int splits = slots / pl.tiles_n;
+    if (splits < 1) splits = 1;
+    if (splits > kb_total / 2) splits = kb_total / 2 > 0 ? kb_total / 2 : 1;
+    pl.kb_per_split = (kb_total + splits - 1) / splits;
+    pl.splits = (kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
+    pl.scratch_bytes = pl.splits > 1 ? static_cast<int64_t>(pl.tiles_n) * pl.mt * kSmallMTileN * 4 : 0;
+    pl.total_bytes = pl.splits > 1 ? pl.scratch_bytes + ((static_cast<int64_t>(pl.tiles_n) * 4 + 15) / 16) * 16 : 0;
+    return pl;
+}
+
+template <int MT, int STAGES>
+int launch_smallm(DeviceState* st, int slot, const int8_t* x, const int8_t* w, SmallMParams p, const SmallMPlan& pl,
+                  cudaStream_t stream)
+{
+    constexpr size_t stage = kSmallMTileN * kBK + ((MT * kBK + 1023) / 1024) * 1024;
+    constexpr size_t smem = STAGES * stage + 1024;
+    auto kernel = smallm_gemm_kernel<MT, STAGES>;
+    if (int rc = ensure_smem(st, slot, kernel, smem)) return rc;
+    CUtensorMap mw, mx;
+    if (int rc = make_operand_map(&mw, w, p.N, p.K, kSmallMTileN)) return rc;
+    if (int rc = make_operand_map(&mx, x, p.M, p.K, MT)) return rc;
+    dim3 grid(pl.tiles_n, pl.splits);
+    kernel<<<grid, kSmallMThreads, smem, stream>>>(mw, mx, p);
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -230,6 +281,7 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
     if (g_forced_variant != VAR_AUTO) return kVariantNames[g_forced_variant];
+    if (kind == 1 && plan_smallm(M, N, K, sms, false).use) return "smallm";
     const int bn = pick_bn(M, N, sms, kind != 2);
     return bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
 }
@@ -275,14 +327,17 @@ int gi8_matmul_i32(const int8_t* x, const int8_t* y, int32_t* out, int64_t M, in
 
 int64_t gi8_matmul_scaled_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
-    (void)M, (void)N, (void)K;
-    return 0;
+    int sms = 148;
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
+    if (g_forced_variant != VAR_AUTO && g_forced_variant != VAR_SMALLM) return 0;
+    const SmallMPlan pl = plan_smallm(M, N, K, sms, g_forced_variant == VAR_SMALLM);
+    return pl.use ? pl.total_bytes : 0;
 }
 
 int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out, int64_t M,
                       int64_t N, int64_t K, void* workspace, int64_t workspace_bytes, void* stream)
 {
-    (void)workspace, (void)workspace_bytes;
     if (int rc = check_common(x, y, out, M, N, K, 2)) return rc;
     if (M == 0 || N == 0) return GI8_OK;
     if (!sx || !sw) return fail(GI8_ERR_INVALID_ARGUMENT, "null scale pointer");
@@ -292,6 +347,29 @@ int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const f
     if (int rc = get_device_state(&st)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (K == 0) return zero_output(out, M * N * 2, s);
+    if (g_forced_variant == VAR_AUTO || g_forced_variant == VAR_SMALLM) {
+        const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, g_forced_variant == VAR_SMALLM);
+        if (pl.use) {
+            SmallMParams q{};
+            q.out = out, q.sx = sx, q.sw = sw, q.status = st->status, q.ldo = N;
+            q.M = (int)M, q.N = (int)N, q.K = (int)K, q.kb_per_split = pl.kb_per_split, q.splits = pl.splits;
+            if (pl.splits > 1) {
+                if (!workspace || workspace_bytes < pl.total_bytes)
+                    return fail(GI8_ERR_WORKSPACE, "this shape needs %lld bytes of zero-filled workspace, got %lld",
+                                (long long)pl.total_bytes, (long long)workspace_bytes);
+                if (reinterpret_cast<uintptr_t>(workspace) % 16)
+                    return fail(GI8_ERR_MISALIGNED, "workspace must be 16-byte aligned");
+                q.scratch = static_cast<int32_t*>(workspace);
+                q.counters = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(workspace) + pl.scratch_bytes);
+            }
+            switch (pl.mt) {
+                case 16: return launch_smallm<16, 6>(st, 24, x, y, q, pl, s);
+                case 32: return launch_smallm<32, 5>(st, 25, x, y, q, pl, s);
+                case 64: return launch_smallm<64, 4>(st, 26, x, y, q, pl, s);
+                default: return launch_smallm<128, 3>(st, 27, x, y, q, pl, s);
+            }
+        }
+    }
     DenseParams p{};
     p.out = out, p.sx = sx, p.sw = sw, p.status = st->status, p.ldo = N, p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.alpha = 1.0f;
@@ -331,19 +409,27 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     p.tiles_n = (int)((N + bn - 1) / bn);
     const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+    // Tuning knob (not part of the ABI): GEMM_INT8_PROMOTION = 0 | 1 | 2 selects the promotion arithmetic.
+    int promo = PROMO_BIAS_X2;
+    if (const char* e = getenv("GEMM_INT8_PROMOTION")) promo = atoi(e);
+    if (make_operand_map(&my, y, N, K, bn)) return GI8_ERR_CUDA;
+#define GI8_LAUNCH_BW(BN_, ST_, PR_, SLOT_)                                                   \
+    do {                                                                                     \
+        constexpr size_t smem = ST_ * (kBM + BN_) * kBK + 1024;                              \
+        auto kernel = blockwise_gemm_kernel<BN_, ST_, PR_>;                                  \
+        if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                        \
+        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, p);                             \
+    } while (0)
     if (bn == 256) {
-        constexpr size_t smem = 4 * (kBM + 256) * kBK + 1024;
-        auto kernel = blockwise_gemm_kernel<256, 4, CVT_MAGIC>;
-        if (int rc = ensure_smem(st, 16, kernel, smem)) return rc;
-        if (int rc = make_operand_map(&my, y, N, K, 256)) return rc;
-        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, p);
+        if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC, 16);
+        else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC_X2, 17);
+        else GI8_LAUNCH_BW(256, 4, PROMO_BIAS_X2, 18);
     } else {
-        constexpr size_t smem = 6 * (kBM + 128) * kBK + 1024;
-        auto kernel = blockwise_gemm_kernel<128, 6, CVT_MAGIC>;
-        if (int rc = ensure_smem(st, 17, kernel, smem)) return rc;
-        if (int rc = make_operand_map(&my, y, N, K, 128)) return rc;
-        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, p);
+        if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC, 19);
+        else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC_X2, 20);
+        else GI8_LAUNCH_BW(128, 6, PROMO_BIAS_X2, 21);
     }
+#undef GI8_LAUNCH_BW
     GI8_CUDA(cudaGetLastError());
     return GI8_OK;
 }

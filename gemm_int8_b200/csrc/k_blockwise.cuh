@@ -21,10 +21,70 @@ namespace gi8 {
 
 constexpr int kBlockwiseThreads = 320;
 
-enum Convert : int {
-    CVT_I2F = 0,    // cvt.rn.f32.s32
-    CVT_MAGIC = 1,  // integer add of 0x4B400000 then fp32 subtract of 12582912 (exact for |P| < 2^22)
+// How a promotion warp turns an int32 partial P (|P| <= 128 * 128 * 128 = 2^21) into fp32 and accumulates it.
+// All three produce bit-identical results: fp32(P) is exact, and the packed f32x2 instructions round each
+// half like the scalar ones.
+enum Promotion : int {
+    PROMO_MAGIC = 0,     // per element: integer add of 0x4B400000, fp32 subtract of 12582912.0, fma
+    PROMO_MAGIC_X2 = 1,  // same, with add.f32x2 / fma.f32x2 on register pairs (half the fp32 instructions)
+    PROMO_BIAS_X2 = 2,   // the TMEM buffer is pre-filled with 0x4B400000 and the MMA accumulates onto it, so the
+                         // value read back is already the float 12582912 + P: only the packed subtract and fma
+                         // remain; the warp re-fills the buffer (tcgen05.st) before handing it back
 };
+
+constexpr uint32_t kMagicBits = 0x4B400000u;  // fp32 12582912.0 = 1.5 * 2^23: adding an integer |P| < 2^22 to the
+constexpr float kMagicF32 = 12582912.0f;      // bit pattern adds P to the value exactly
+
+GI8_DEVICE uint64_t pack_f32x2(uint32_t lo_bits, uint32_t hi_bits)
+{
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo_bits), "r"(hi_bits));
+    return r;
+}
+
+GI8_DEVICE void unpack_f32x2(uint64_t v, float& lo, float& hi)
+{
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+
+GI8_DEVICE uint64_t add_f32x2(uint64_t a, uint64_t b)
+{
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
+GI8_DEVICE uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c)
+{
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
+// Stores one 32-bit value to N consecutive TMEM columns (N = 8 or 16) of the warp's 32 lanes.
+template <int N>
+GI8_DEVICE void tmem_fill_32x32b(uint32_t taddr, uint32_t v)
+{
+    if constexpr (N == 16) {
+        asm volatile(
+            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+            "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v)
+            : "memory");
+    } else {
+        static_assert(N == 8, "fill width");
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v)
+                     : "memory");
+    }
+}
+
+template <int N>
+GI8_DEVICE void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[N])
+{
+    if constexpr (N == 16) tmem_ld_32x32b_x16(taddr, r);
+    else tmem_ld_32x32b_x8(taddr, r);
+}
+
+GI8_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 struct BlockwiseParams {
     void* out;        // bf16 [M,N], leading dimension ldo
@@ -37,24 +97,15 @@ struct BlockwiseParams {
     int vec_ok;  // out is 16-byte aligned and ldo % 8 == 0
 };
 
-template <int CVT>
-GI8_DEVICE float partial_to_f32(uint32_t v)
-{
-    if constexpr (CVT == CVT_I2F) {
-        return __int2float_rn(static_cast<int32_t>(v));
-    } else {
-        return __uint_as_float(v + 0x4B400000u) - 12582912.0f;
-    }
-}
-
-template <int BN, int STAGES, int CVT>
+template <int BN, int STAGES, int PROMO>
 __global__ void __launch_bounds__(kBlockwiseThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                       const BlockwiseParams p)
 {
     static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
     constexpr int CW = BN / 2;  // columns per promotion warp
-    constexpr int kLd = CW > 64 ? 16 : 32;  // columns per tcgen05.ld (register budget: CW accumulators + kLd)
+    constexpr int kLd = CW > 64 ? 8 : 16;  // columns per tcgen05.ld; two chunks live at a time (register budget)
+    constexpr bool kBias = PROMO == PROMO_BIAS_X2;
     constexpr uint32_t kBytesA = kBM * kBK;
     constexpr uint32_t kBytesB = BN * kBK;
     constexpr uint32_t kStageBytes = kBytesA + kBytesB;
@@ -141,7 +192,8 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     const uint32_t ph = (it / STAGES) & 1;
                     const uint32_t buf = it & 1;
                     const uint32_t bph = (it >> 1) & 1;
-                    if (!wait_or_abort(&bar_part_empty[buf], bph ^ 1, &abort_flag) ||
+                    // kBias: the buffer's first hand-over is the promotion warps' initial fill (one extra phase)
+                    if (!wait_or_abort(&bar_part_empty[buf], kBias ? bph : (bph ^ 1), &abort_flag) ||
                         !wait_or_abort(&bar_full[s], ph, &abort_flag)) {
                         raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
                         ok = false;
@@ -153,7 +205,8 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     const uint64_t da = make_smem_desc_k128(a_addr);
                     const uint64_t db = make_smem_desc_k128(a_addr + kBytesA);
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k) umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, k != 0);
+                    for (int k = 0; k < kBK / kUmmaK; ++k)
+                        umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kBias || k != 0) ? 1u : 0u);
                     umma_commit(&bar_empty[s]);
                     umma_commit(&bar_part_full[buf]);
                 }
@@ -163,8 +216,26 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         // ------------------------------------------------------------------ promotion + epilogue warps
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         uint32_t it = 0;
         bool ok = true;
+
+        if constexpr (kBias) {
+            // Pre-fill this warp's part of both partial buffers with the magic constant, then hand them over.
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                for (int c = 0; c < CW; c += kLd) tmem_fill_32x32b<kLd>(tmem_base + lane_base + b * BN + half * CW + c, kMagicBits);
+            }
+            tmem_st_wait();
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bar_part_empty[0]);
+                mbar_arrive(&bar_part_empty[1]);
+            }
+        }
+
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             int mb, nb;
             tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
@@ -176,9 +247,10 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             const float* sa_row = p.sa + static_cast<int64_t>(row_ok ? row : 0) * p.ld_sa;
             const float* sw_row = p.sw + static_cast<int64_t>(cols_ok ? col_base / 128 : 0) * p.ld_sw;
 
-            float acc[CW];
+            // fp32 accumulators, two per 64-bit register pair: acc2[j] = {column 2j, column 2j + 1}
+            uint64_t acc2[CW / 2];
 #pragma unroll
-            for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
+            for (int j = 0; j < CW / 2; ++j) acc2[j] = 0ull;
 
             float sa_next = __ldg(sa_row);
             float sw_next = __ldg(sw_row);
@@ -190,22 +262,50 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     sa_next = __ldg(sa_row + kb + 1);
                     sw_next = __ldg(sw_row + kb + 1);
                 }
+                const uint64_t t2 = pack_f32x2(__float_as_uint(t), __float_as_uint(t));
+                const uint64_t neg_magic2 = pack_f32x2(__float_as_uint(-kMagicF32), __float_as_uint(-kMagicF32));
                 if (!wait_or_abort(&bar_part_full[buf], bph, &abort_flag)) {
                     if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
                     ok = false;
                     break;
                 }
                 tcgen05_fence_after_sync();
-                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN + half * CW;
+                const uint32_t taddr = tmem_base + lane_base + buf * BN + half * CW;
+
+                // Software pipeline over 16-column chunks: the load of chunk c + 1 is in flight while chunk c
+                // is converted and accumulated.
+                uint32_t va[kLd], vb[kLd];
+                auto consume = [&](const uint32_t (&v)[kLd], int c) {
 #pragma unroll
-                for (int c = 0; c < CW; c += kLd) {
-                    uint32_t v[kLd];
-                    if constexpr (kLd == 32) tmem_ld_32x32b_x32(taddr + c, v);
-                    else tmem_ld_32x32b_x16(taddr + c, v);
+                    for (int j = 0; j < kLd; j += 2) {
+                        if constexpr (PROMO == PROMO_MAGIC) {
+                            float lo, hi;
+                            unpack_f32x2(acc2[(c + j) / 2], lo, hi);
+                            lo = fmaf(__uint_as_float(v[j] + kMagicBits) - kMagicF32, t, lo);
+                            hi = fmaf(__uint_as_float(v[j + 1] + kMagicBits) - kMagicF32, t, hi);
+                            acc2[(c + j) / 2] = pack_f32x2(__float_as_uint(lo), __float_as_uint(hi));
+                        } else {
+                            const uint32_t b0 = kBias ? v[j] : v[j] + kMagicBits;
+                            const uint32_t b1 = kBias ? v[j + 1] : v[j + 1] + kMagicBits;
+                            const uint64_t pf = add_f32x2(pack_f32x2(b0, b1), neg_magic2);  // exact fp32(P)
+                            acc2[(c + j) / 2] = fma_f32x2(pf, t2, acc2[(c + j) / 2]);
+                        }
+                    }
+                };
+                tmem_ld_chunk<kLd>(taddr, va);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < CW; c += 2 * kLd) {
+                    tmem_ld_chunk<kLd>(taddr + c + kLd, vb);
+                    if constexpr (kBias) tmem_fill_32x32b<kLd>(taddr + c, kMagicBits);
+                    consume(va, c);
                     tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < kLd; ++j) acc[c + j] = fmaf(partial_to_f32<CVT>(v[j]), t, acc[c + j]);
+                    if (c + 2 * kLd < CW) tmem_ld_chunk<kLd>(taddr + c + 2 * kLd, va);
+                    if constexpr (kBias) tmem_fill_32x32b<kLd>(taddr + c + kLd, kMagicBits);
+                    consume(vb, c + kLd);
+                    if (c + 2 * kLd < CW) tmem_ld_wait();
                 }
+                if constexpr (kBias) tmem_st_wait();
                 tcgen05_fence_before_sync();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_part_empty[buf]);
@@ -216,14 +316,22 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col_base;
                 if (col_base + CW <= p.N && p.vec_ok) {
 #pragma unroll
-                    for (int j = 0; j < CW; j += 8)
+                    for (int j = 0; j < CW; j += 8) {
+                        float f[8];
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) unpack_f32x2(acc2[j / 2 + q], f[2 * q], f[2 * q + 1]);
                         *reinterpret_cast<uint4*>(dst + j) =
-                            make_uint4(pack_bf16x2(acc[j], acc[j + 1]), pack_bf16x2(acc[j + 2], acc[j + 3]),
-                                       pack_bf16x2(acc[j + 4], acc[j + 5]), pack_bf16x2(acc[j + 6], acc[j + 7]));
+                            make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
+                                       pack_bf16x2(f[6], f[7]));
+                    }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < CW; ++j)
-                        if (col_base + j < p.N) dst[j] = to_bf16_bits(acc[j]);
+                    for (int j = 0; j < CW; j += 2) {
+                        float lo, hi;
+                        unpack_f32x2(acc2[j / 2], lo, hi);
+                        if (col_base + j < p.N) dst[j] = to_bf16_bits(lo);
+                        if (col_base + j + 1 < p.N) dst[j + 1] = to_bf16_bits(hi);
+                    }
                 }
             }
             __syncwarp();

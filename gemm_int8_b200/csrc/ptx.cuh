@@ -86,7 +86,7 @@ GI8_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity)
 // Wall-clock limit of one wait.  Generous against any legitimate stall (a whole kernel takes
 // milliseconds), short enough that a protocol bug ends the kernel instead of hanging the GPU.
 #ifndef GI8_WAIT_LIMIT_NS
-#define GI8_WAIT_LIMIT_NS 2000000000ull
+#define GI8_WAIT_LIMIT_NS 250000000ull
 #endif
 
 // Bounded wait for the phase with the given parity to complete.  Returns false on timeout.
@@ -271,6 +271,14 @@ GI8_DEVICE void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
         : "r"(taddr)
         : "memory");
+}
+
+GI8_DEVICE void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
 }
 
 GI8_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }

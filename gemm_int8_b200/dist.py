@@ -1,0 +1,102 @@
+"""Column-wise (N) sharding of a large GEMM over the GPUs of one box, and the gather of the bf16 slices.
+
+The reference is single-GPU (no collective call sites anywhere in its tree).  Output columns of
+``x @ y.T`` are independent, so rank r keeps rows ``[n0, n1)`` of the weight ``y`` (and the matching rows
+of the 128x128-block weight scales), every rank holds the full activation ``x``, and each computes its
+``[M, n1 - n0]`` slice with the unchanged single-GPU kernel: no communication inside the GEMM.  Only when
+the caller needs the whole matrix are the slices exchanged, with one NCCL all-gather over NVLink.
+
+One process per GPU; ``torch.distributed`` must be initialised by the caller (backend "nccl" on GPUs;
+the index logic also runs under "gloo" on CPU tensors, which is how it is tested without GPUs).
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+import torch.distributed as dist
+
+KBLOCK = 128
+
+
+def shard_bounds(N: int, world: int, rank: int, block: int = KBLOCK) -> tuple[int, int]:
+    """Rows [n0, n1) of the weight owned by `rank`: whole 128-row blocks, as even as possible, so that a
+    shard never splits a weight-scale block.  Trailing ranks may own fewer (or zero) rows."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world of {world}")
+    nb = -(-N // block)
+    base, extra = divmod(nb, world)
+    b0 = rank * base + min(rank, extra)
+    b1 = b0 + base + (1 if rank < extra else 0)
+    return min(b0 * block, N), min(b1 * block, N)
+
+
+def shard_weight(y: torch.Tensor, w_scale: Optional[torch.Tensor], rank: int, world: int):
+    """Returns this rank's (y rows, weight-scale rows) as contiguous tensors."""
+    n0, n1 = shard_bounds(y.shape[0], world, rank)
+    ys = y[n0:n1].contiguous()
+    if w_scale is None:
+        return ys, None
+    if w_scale.dim() == 1:  # per-output-channel scales [N]
+        return ys, w_scale[n0:n1].contiguous()
+    return ys, w_scale[n0 // KBLOCK: -(-n1 // KBLOCK)].contiguous()
+
+
+def uniform_shards(N: int, world: int) -> bool:
+    sizes = {shard_bounds(N, world, r)[1] - shard_bounds(N, world, r)[0] for r in range(world)}
+    return len(sizes) == 1
+
+
+def all_gather_slices(local: torch.Tensor, out: Optional[torch.Tensor] = None, group=None) -> torch.Tensor:
+    """All-gathers equal-sized ``[M, n_local]`` slices into ``[world, M, n_local]`` (block layout: slice r is
+    the r-th column block of the full matrix).  One collective, no copy; `out` may be preallocated."""
+    world = dist.get_world_size(group)
+    if out is None:
+        out = torch.empty((world, *local.shape), dtype=local.dtype, device=local.device)
+    # concatenation along dim 0 of the flattened view == stacking into [world, M, n_local]
+    dist.all_gather_into_tensor(out.view(world * local.shape[0], *local.shape[1:]), local.contiguous(), group=group)
+    return out
+
+
+def assemble_row_major(blocks: torch.Tensor) -> torch.Tensor:
+    """``[world, M, n_local]`` block layout -> row-major ``[M, world * n_local]`` (one permuting copy)."""
+    g, M, n = blocks.shape
+    return blocks.permute(1, 0, 2).reshape(M, g * n)
+
+
+def all_gather_ragged(local: torch.Tensor, N: int, group=None) -> torch.Tensor:
+    """Gather for shard widths that differ between ranks: every slice is padded to the widest shard, gathered
+    with the same single collective, and the padding is dropped while assembling row-major ``[M, N]``."""
+    world = dist.get_world_size(group)
+    M = local.shape[0]
+    bounds = [shard_bounds(N, world, r) for r in range(world)]
+    widest = max(n1 - n0 for n0, n1 in bounds)
+    padded = local
+    if local.shape[1] != widest:
+        padded = torch.zeros((M, widest), dtype=local.dtype, device=local.device)
+        padded[:, : local.shape[1]] = local
+    blocks = all_gather_slices(padded, group=group)
+    return torch.cat([blocks[r, :, : n1 - n0] for r, (n0, n1) in enumerate(bounds)], dim=1)
+
+
+def matmul_blockwise_nsharded(x_q: torch.Tensor, w_q_shard: torch.Tensor, x_scale: torch.Tensor,
+                              w_scale_shard: torch.Tensor, N: int, gather: bool = True, row_major: bool = True,
+                              group=None, compute: Optional[Callable] = None) -> torch.Tensor:
+    """Blockwise W8A8 GEMM with the weight sharded over N.
+
+    Each rank passes the full activations and ITS weight shard (see `shard_weight`).  With ``gather=False``
+    the local ``[M, n_local]`` slice is returned and nothing is communicated.  With ``gather=True`` every rank
+    gets the full result: row-major ``[M, N]`` (``row_major=True``, costs one permuting copy) or the
+    ``[world, M, n_local]`` block layout straight out of the collective.
+    `compute` replaces the local GEMM (tests inject a CPU checker there); by default it is the CUDA op.
+    """
+    if compute is None:
+        from . import matmul_blockwise as compute
+    local = compute(x_q, w_q_shard, x_scale, w_scale_shard)
+    if not gather:
+        return local
+    world = dist.get_world_size(group)
+    if uniform_shards(N, world):
+        blocks = all_gather_slices(local, group=group)
+        return assemble_row_major(blocks) if row_major else blocks
+    return all_gather_ragged(local, N, group=group)
