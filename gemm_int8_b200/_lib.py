@@ -31,6 +31,7 @@ SYMBOLS = {
     "gi8_matmul_i32": (_i, [_p, _p, _p, _i64, _i64, _i64, _p]),
     "gi8_matmul_scaled": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p, _i64, _p]),
     "gi8_matmul_scaled_workspace_bytes": (_i64, [_i64, _i64, _i64]),
+    "gi8_matmul_scaled_static": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "gi8_matmul_blockwise": (_i, [_p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p]),
     "gi8_force_variant": (_i, [ctypes.c_char_p]),
     "gi8_pick_variant": (ctypes.c_char_p, [_i, _i64, _i64, _i64]),
@@ -42,7 +43,7 @@ def load(path: str = LIB_PATH) -> ctypes.CDLL:
     if not os.path.exists(path):
         raise ImportError(
             f"Could not find the compiled CUDA library {path}; build it with "
-            "`python -m gemm_int8_b200._build` (needs nvcc). There is no CPU fallback."
+            "`python gemm_int8_b200/_build.py` (needs nvcc). There is no CPU fallback."
         )
     lib = ctypes.CDLL(path)
     for name, (res, args) in SYMBOLS.items():

@@ -252,6 +252,30 @@ int launch_smallm(DeviceState* st, int slot, const int8_t* x, const int8_t* w, S
     return GI8_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Fixed scratch for gi8_matmul_scaled_static.  In host code the name below is only a handle for the
+// runtime, not a device address: the address a kernel can use comes from cudaGetSymbolAddress, looked up
+// once per device (each device has its own copy of the array) and cached here.
+// ---------------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_scratch[GI8_STATIC_SCRATCH_BYTES];
+void* g_static_scratch_ptr[kMaxDevices] = {};
+
+int get_static_scratch(void** out)
+{
+    int dev = 0;
+    GI8_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(GI8_ERR_UNSUPPORTED_DEVICE, "device index %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (!g_static_scratch_ptr[dev]) {
+        void* ptr = nullptr;
+        GI8_CUDA(cudaGetSymbolAddress((void**)&ptr, g_static_scratch));  // device `dev` is current here
+        if (!ptr) return fail(GI8_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the static scratch");
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return GI8_OK;
+}
+
 }  // namespace
 
 extern "C" {
@@ -375,6 +399,45 @@ int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const f
     p.alpha = 1.0f;
     p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
     return dispatch_dense<EPI_ROWCOL_BF16>(st, x, y, p, s);
+}
+
+int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out, int64_t M,
+                             int64_t N, int64_t K, void* stream)
+{
+    if (int rc = check_common(x, y, out, M, N, K, 2)) return rc;
+    if (M == 0 || N == 0) return GI8_OK;
+    if (M > 128)
+        return fail(GI8_ERR_UNSUPPORTED_SHAPE, "gi8_matmul_scaled_static covers M <= 128 only (got M=%lld); use "
+                    "gi8_matmul_scaled", (long long)M);
+    if (!sx || !sw) return fail(GI8_ERR_INVALID_ARGUMENT, "null scale pointer");
+    if (reinterpret_cast<uintptr_t>(sx) % 4 || reinterpret_cast<uintptr_t>(sw) % 4)
+        return fail(GI8_ERR_MISALIGNED, "scale pointers must be 4-byte aligned");
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (K == 0) return zero_output(out, M * N * 2, s);
+    const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, true);
+    if (pl.total_bytes > GI8_STATIC_SCRATCH_BYTES)
+        return fail(GI8_ERR_UNSUPPORTED_SHAPE, "this shape needs %lld bytes of scratch but the static scratch holds "
+                    "%lld (GI8_STATIC_SCRATCH_BYTES); use gi8_matmul_scaled with a caller-owned workspace",
+                    (long long)pl.total_bytes, (long long)GI8_STATIC_SCRATCH_BYTES);
+    SmallMParams q{};
+    q.out = out, q.sx = sx, q.sw = sw, q.status = st->status, q.ldo = N;
+    q.M = (int)M, q.N = (int)N, q.K = (int)K, q.kb_per_split = pl.kb_per_split, q.splits = pl.splits;
+    if (pl.splits > 1) {
+        void* base = nullptr;
+        if (int rc = get_static_scratch(&base)) return rc;
+        // The array holds the previous call's leftovers: clear the part this call accumulates into.
+        GI8_CUDA(cudaMemsetAsync(base, 0, static_cast<size_t>(pl.total_bytes), s));
+        q.scratch = static_cast<int32_t*>(base);
+        q.counters = reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(base) + pl.scratch_bytes);
+    }
+    switch (pl.mt) {
+        case 16: return launch_smallm<16, 6>(st, 24, x, y, q, pl, s);
+        case 32: return launch_smallm<32, 5>(st, 25, x, y, q, pl, s);
+        case 64: return launch_smallm<64, 4>(st, 26, x, y, q, pl, s);
+        default: return launch_smallm<128, 3>(st, 27, x, y, q, pl, s);
+    }
 }
 
 int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,

@@ -84,6 +84,33 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
                          int64_t ld_sw, void* out_bf16, int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * Allocation-free variant of gi8_matmul_scaled for small token counts (M <= 128), same arithmetic and result.
+ * It has no counterpart in the reference.
+ *
+ * Who it is for: hosts that may not allocate device memory around this call -- a serving runtime that handed
+ * all of HBM to its own pool at start-up (a cudaMalloc there fails or fragments the pool), a decode loop that
+ * cannot afford the device-wide synchronisation cudaMalloc/cudaFree imply, or a plain C caller that has no
+ * device allocator to make the scratch buffer gi8_matmul_scaled asks for.  Here the split-K scratch lives in
+ * a fixed GI8_STATIC_SCRATCH_BYTES array inside the library's device image (every GPU that loads the library
+ * holds those bytes until the process exits); the caller passes only inputs and outputs, and the call
+ * performs no cudaMalloc, cudaFree or other allocating routine.
+ *
+ * Limits and rules
+ *   - M must be in [1, 128]; the scratch the shape needs, ceil(N/128) * MT * 512 + 4 * ceil(N/128) bytes
+ *     (MT = M rounded up to 16, 32, 64 or 128), must fit GI8_STATIC_SCRATCH_BYTES.  Larger shapes are
+ *     refused with GI8_ERR_UNSUPPORTED_SHAPE and a message naming both numbers; nothing is launched.
+ *   - The first call on each device looks up the array's device address (once, with that device current).
+ *     Make that first call outside any stream capture.
+ *   - Every call on a device shares the one array, and the array keeps whatever the previous call left:
+ *     the part a call uses is cleared on `stream` before its kernel runs.  Two calls whose GPU work can
+ *     overlap (different streams, or different host threads on different streams) race on it -- serialise
+ *     them on one stream or with events.
+ */
+#define GI8_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out_bf16,
+                             int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
  * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted
  * per-shape dispatch that replaces the reference's shape table (csrc/kernels/gemm.cu:136-161).
  * Names: "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "auto".  Returns GI8_ERR_INVALID_ARGUMENT
