@@ -43,6 +43,7 @@ WORKLOADS = {
     "plain": (1024, 4096, 4096, "plain"),
     "nshard": (16384, 57344, 8192, "blockwise"),
     "square8192": (8192, 8192, 8192, "plain"),
+    "decode": (16, 4096, 4096, "scaled"),
 }
 
 
@@ -137,6 +138,8 @@ def make_inputs(name: str, world: int, rank: int):
         return workloads.blockwise_prefill(M, N, K, seed=2001 + 10 * rank), kind
     if name == "nshard":
         return workloads.nshard(M, N, K), kind
+    if name == "decode":
+        return workloads.decode(M, N, K), kind
     x, y, _ = workloads.plain(M, N, K, seed=1001 if name == "plain" else 6001)
     return (x, y), kind
 
@@ -158,6 +161,8 @@ def cpu_baseline(name: str, budget_s: float = 12.0):
     def run_once():
         if kind == "blockwise":
             O.c_matmul_blockwise(x, inputs[1], inputs[2][:rows].contiguous(), inputs[3])
+        elif kind == "scaled":
+            O.c_matmul_scaled(x, inputs[1], inputs[2][:rows].contiguous(), inputs[3])
         else:
             O.c_matmul(x, inputs[1], 1.0)
 
@@ -191,6 +196,9 @@ def run_reference(args, rank):
     if kind == "blockwise":
         inp = workloads.blockwise_prefill(rows, N, K) if name == "blockwise_prefill" else workloads.nshard(rows, N, K)
         fn = lambda: O.c_matmul_blockwise(inp[0], inp[1], inp[2], inp[3])  # noqa: E731
+    elif kind == "scaled":
+        inp = workloads.decode(rows, N, K)
+        fn = lambda: O.c_matmul_scaled(inp[0], inp[1], inp[2], inp[3])  # noqa: E731
     else:
         inp = workloads.plain(rows, N, K)
         fn = lambda: O.c_matmul(inp[0], inp[1], 1.0)  # noqa: E731
@@ -223,11 +231,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="blockwise_prefill", choices=sorted(WORKLOADS))
+    ap.add_argument("--M", type=int, default=0, help="override the workload's M")
+    ap.add_argument("--N", type=int, default=0, help="override the workload's N")
+    ap.add_argument("--K", type=int, default=0, help="override the workload's K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.M or args.N or args.K:
+        m, n, k, kd = WORKLOADS[args.workload]
+        WORKLOADS[args.workload] = (args.M or m, args.N or n, args.K or k, kd)
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -266,12 +280,17 @@ def main():
     # Several rotating copies of the operands so that consecutive steps never reuse lines left in L2
     # (in addition to the explicit flush below).
     bytes_one = sum(t.numel() * t.element_size() for t in inputs) + 2 * M * n_local
-    copies = 1 if bytes_one > 300e6 else 3
+    copies = 1 if bytes_one > 300e6 else max(3, int(300e6 // bytes_one) + 1)
+    copies = min(copies, 24)
     dev_sets = [[t.to(dev) for t in inputs] for _ in range(copies)]
-    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    # L2 flush by READING a 256 MiB buffer: it leaves clean lines behind, so the timed kernel does not pay for
+    # write-backs of somebody else's dirty data (a write-based flush would add that DRAM traffic to it).
+    flush_buf = torch.zeros(256 << 20, dtype=torch.uint8, device=dev).view(torch.int64)
 
     if kind == "blockwise":
         op = lambda s: g.matmul_blockwise(s[0], s[1], s[2], s[3])  # noqa: E731
+    elif kind == "scaled":
+        op = lambda s: g.matmul_scaled(s[0], s[1], s[2], s[3])  # noqa: E731
     else:
         op = lambda s: g.matmul(s[0], s[1], 1.0)  # noqa: E731
 
@@ -287,7 +306,7 @@ def main():
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
         for i in range(n):
-            flush_buf.fill_(i & 0xFF)  # evicts L2 (256 MiB > 126 MB)
+            flush_buf.max()  # reads 256 MiB: evicts L2 (126 MB) without leaving dirty lines
             starts[i].record()
             op(dev_sets[i % copies])
             ends[i].record()
@@ -322,7 +341,7 @@ def main():
 
         def e2e_step():
             s = [t.to(dev, non_blocking=True) for t in host_in]
-            out = g.matmul_blockwise(*s) if kind == "blockwise" else g.matmul(s[0], s[1], 1.0)
+            out = op(s)
             host_out.copy_(out, non_blocking=True)
 
         for _ in range(3):
@@ -354,19 +373,29 @@ def main():
         achieved = per_gpu_ops / (kernel_ms * 1e-3) / 1e12
         int8_peak = 2.0 * peaks["bf16_tflops"]
         cb = None if args.no_cpu_baseline else cpu_baseline(name)
+        n_scales = sum(t.numel() for t in inputs[2:]) if len(inputs) > 2 else 0
+        algo_bytes = M * K + n_local * K + 2 * M * n_local + 4 * n_scales
+        if kind == "scaled" and M <= 64:
+            gbs = algo_bytes / (kernel_ms * 1e-3) / 1e9
+            roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": gbs / peaks["hbm_gbs"], "traffic": None,
+                        "note": f"algorithmic bytes {algo_bytes} per launch; peak = {peak_kind} copy bandwidth "
+                                f"({peaks['hbm_gbs']} GB/s) of {peak_kind}; min step {min(times):.4f} ms"}
+        else:
+            roofline = {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
+                        "frac": achieved / int8_peak, "traffic": None,
+                        "note": f"int8 TOP/s of the GEMM launch; peak = 2 x {peak_kind} bf16 burst "
+                                f"({peaks['bf16_tflops']} TFLOP/s) of {peak_kind}; min step {min(times):.4f} ms"}
         line = {
             "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong" if nshard else "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
             "config": {"workload": name, "M": M, "N": N, "K": K, "kind": kind, "per_gpu_N": n_local,
-                       "variant": g.pick_variant(2 if kind == "blockwise" else 0, M, n_local, K),
-                       "l2": "flushed between steps (256 MiB write) and operands rotated over "
+                       "variant": g.pick_variant({"blockwise": 2, "scaled": 1}.get(kind, 0), M, n_local, K),
+                       "l2": "flushed between steps (256 MiB read) and operands rotated over "
                              f"{copies} copies", "parallelism": f"dp{world}" if not nshard else f"nshard{world}+allgather",
                        "frac_of_nominal_int8_peak_4500": tops / world / 4500.0 if not nshard else None},
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": int8_peak, "unit": "TFLOP/s",
-                         "frac": achieved / int8_peak, "traffic": None,
-                         "note": f"int8 TOP/s of the GEMM launch; peak = 2 x {peak_kind} bf16 burst "
-                                 f"({peaks['bf16_tflops']} TFLOP/s) of {peak_kind}; min step {min(times):.4f} ms"},
+            "roofline": roofline,
             "cpu_baseline": cb,
             "e2e": e2e,
             "gpu_launches": args.steps,

@@ -42,8 +42,9 @@ int fail(int code, const char* fmt, ...)
 // Kernel status word: one instance per device (module-scope device variable).
 __device__ uint32_t g_kernel_status;
 
-enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM };
-const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm"};
+enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM, VAR_SMALLM_CLUSTER };
+const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "smallm_cluster"};
+constexpr int kNumVariants = 6;
 int g_forced_variant = VAR_AUTO;
 
 struct DeviceState {
@@ -216,7 +217,7 @@ struct SmallMPlan {
 
 constexpr int kSmallMMaxM = 64;  // the automatic dispatch sends M <= 64 to the small-M kernel
 
-SmallMPlan plan_smallm(int64_t M, int64_t N, int64_t K, int sms, bool forced)
+SmallMPlan plan_smallm(int64_t M, int64_t N, int64_t K, int sms, bool forced, int max_splits = 1 << 30)
 {
     SmallMPlan pl{};
     pl.use = (M >= 1) && (forced ? M <= 128 : M <= kSmallMMaxM) && K > 0 && N > 0;
@@ -228,6 +229,7 @@ SmallMPlan plan_smallm(int64_t M, int64_t N, int64_t K, int sms, bool forced)
     int splits = slots / pl.tiles_n;
     if (splits < 1) splits = 1;
     if (splits > kb_total / 2) splits = kb_total / 2 > 0 ? kb_total / 2 : 1;
+    if (splits > max_splits) splits = max_splits;
     pl.kb_per_split = (kb_total + splits - 1) / splits;
     pl.splits = (kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
     pl.scratch_bytes = pl.splits > 1 ? static_cast<int64_t>(pl.tiles_n) * pl.mt * kSmallMTileN * 4 : 0;
@@ -249,6 +251,35 @@ int launch_smallm(DeviceState* st, int slot, const int8_t* x, const int8_t* w, S
     dim3 grid(pl.tiles_n, pl.splits);
     kernel<<<grid, kSmallMThreads, smem, stream>>>(mw, mx, p);
     GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
+}
+
+constexpr int kMaxClusterSplits = 8;  // portable thread-block cluster size
+
+template <int MT, int STAGES>
+int launch_smallm_cluster(DeviceState* st, int slot, const int8_t* x, const int8_t* w, SmallMParams p,
+                          const SmallMPlan& pl, cudaStream_t stream)
+{
+    constexpr size_t stage = kSmallMTileN * kBK + ((MT * kBK + 1023) / 1024) * 1024;
+    constexpr size_t smem = STAGES * stage + 1024;
+    auto kernel = smallm_cluster_kernel<MT, STAGES>;
+    if (int rc = ensure_smem(st, slot, kernel, smem)) return rc;
+    CUtensorMap mw, mx;
+    if (int rc = make_operand_map(&mw, w, p.N, p.K, kSmallMTileN)) return rc;
+    if (int rc = make_operand_map(&mx, x, p.M, p.K, MT)) return rc;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(pl.tiles_n, pl.splits, 1);
+    cfg.blockDim = dim3(kSmallMThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = pl.splits;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, p));
     return GI8_OK;
 }
 
@@ -290,7 +321,7 @@ int gi8_force_variant(const char* name)
         g_forced_variant = VAR_AUTO;
         return GI8_OK;
     }
-    for (int i = 0; i < 5; ++i)
+    for (int i = 0; i < kNumVariants; ++i)
         if (!strcmp(name, kVariantNames[i])) {
             g_forced_variant = i;
             return GI8_OK;
@@ -305,7 +336,7 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
     if (g_forced_variant != VAR_AUTO) return kVariantNames[g_forced_variant];
-    if (kind == 1 && plan_smallm(M, N, K, sms, false).use) return "smallm";
+    if (kind == 1 && plan_smallm(M, N, K, sms, false).use) return "smallm_cluster";
     const int bn = pick_bn(M, N, sms, kind != 2);
     return bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
 }
@@ -354,8 +385,8 @@ int64_t gi8_matmul_scaled_workspace_bytes(int64_t M, int64_t N, int64_t K)
     int sms = 148;
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
-    if (g_forced_variant != VAR_AUTO && g_forced_variant != VAR_SMALLM) return 0;
-    const SmallMPlan pl = plan_smallm(M, N, K, sms, g_forced_variant == VAR_SMALLM);
+    if (g_forced_variant != VAR_SMALLM) return 0;  // only the scratch variant needs a workspace
+    const SmallMPlan pl = plan_smallm(M, N, K, sms, true);
     return pl.use ? pl.total_bytes : 0;
 }
 
@@ -371,8 +402,22 @@ int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const f
     if (int rc = get_device_state(&st)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (K == 0) return zero_output(out, M * N * 2, s);
-    if (g_forced_variant == VAR_AUTO || g_forced_variant == VAR_SMALLM) {
-        const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, g_forced_variant == VAR_SMALLM);
+    if (g_forced_variant == VAR_AUTO || g_forced_variant == VAR_SMALLM_CLUSTER) {
+        const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, g_forced_variant == VAR_SMALLM_CLUSTER, kMaxClusterSplits);
+        if (pl.use) {
+            SmallMParams q{};
+            q.out = out, q.sx = sx, q.sw = sw, q.status = st->status, q.ldo = N;
+            q.M = (int)M, q.N = (int)N, q.K = (int)K, q.kb_per_split = pl.kb_per_split, q.splits = pl.splits;
+            switch (pl.mt) {
+                case 16: return launch_smallm_cluster<16, 6>(st, 28, x, y, q, pl, s);
+                case 32: return launch_smallm_cluster<32, 5>(st, 29, x, y, q, pl, s);
+                case 64: return launch_smallm_cluster<64, 4>(st, 30, x, y, q, pl, s);
+                default: return launch_smallm_cluster<128, 3>(st, 31, x, y, q, pl, s);
+            }
+        }
+    }
+    if (g_forced_variant == VAR_SMALLM) {
+        const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, true);
         if (pl.use) {
             SmallMParams q{};
             q.out = out, q.sx = sx, q.sw = sw, q.status = st->status, q.ldo = N;
@@ -472,8 +517,9 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     p.tiles_n = (int)((N + bn - 1) / bn);
     const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
-    // Tuning knob (not part of the ABI): GEMM_INT8_PROMOTION = 0 | 1 | 2 selects the promotion arithmetic.
-    int promo = PROMO_BIAS_X2;
+    // Tuning knob (not part of the ABI): GEMM_INT8_PROMOTION = 0 | 1 | 2 selects the promotion arithmetic
+    // (3 and 4 are measurement-only ablations that produce wrong results).
+    int promo = PROMO_I2F;
     if (const char* e = getenv("GEMM_INT8_PROMOTION")) promo = atoi(e);
     if (make_operand_map(&my, y, N, K, bn)) return GI8_ERR_CUDA;
 #define GI8_LAUNCH_BW(BN_, ST_, PR_, SLOT_)                                                   \
@@ -483,14 +529,30 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
         if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                        \
         kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, p);                             \
     } while (0)
+    if (promo < PROMO_MAGIC || promo > PROMO_ABLATE_CVT_ONLY) promo = PROMO_I2F;
+#ifndef GI8_ENABLE_ABLATIONS
+    if (promo > PROMO_I2F) promo = PROMO_I2F;  // the ablation kernels (wrong results) exist only in tuning builds
+#endif
     if (bn == 256) {
-        if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC, 16);
-        else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC_X2, 17);
-        else GI8_LAUNCH_BW(256, 4, PROMO_BIAS_X2, 18);
+        if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC, 13);
+        else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC_X2, 14);
+#ifdef GI8_ENABLE_ABLATIONS
+        else if (promo == PROMO_ABLATE_HANDSHAKE) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_HANDSHAKE, 15);
+        else if (promo == PROMO_ABLATE_LOAD) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_LOAD, 16);
+        else if (promo == PROMO_ABLATE_SCALES) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_SCALES, 11);
+        else if (promo == PROMO_ABLATE_MATH) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_MATH, 12);
+        else if (promo == PROMO_ABLATE_FMA_ONLY) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_FMA_ONLY, 9);
+        else if (promo == PROMO_ABLATE_CVT_ONLY) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_CVT_ONLY, 10);
+#endif
+        else GI8_LAUNCH_BW(256, 4, PROMO_I2F, 17);
     } else {
-        if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC, 19);
-        else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC_X2, 20);
-        else GI8_LAUNCH_BW(128, 6, PROMO_BIAS_X2, 21);
+        if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC, 18);
+        else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC_X2, 19);
+#ifdef GI8_ENABLE_ABLATIONS
+        else if (promo == PROMO_ABLATE_HANDSHAKE) GI8_LAUNCH_BW(128, 6, PROMO_ABLATE_HANDSHAKE, 20);
+        else if (promo == PROMO_ABLATE_LOAD) GI8_LAUNCH_BW(128, 6, PROMO_ABLATE_LOAD, 21);
+#endif
+        else GI8_LAUNCH_BW(128, 6, PROMO_I2F, 22);
     }
 #undef GI8_LAUNCH_BW
     GI8_CUDA(cudaGetLastError());

@@ -4,36 +4,65 @@
 // There is no such path in the reference (its epilogue applies one scalar, csrc/kernels/gemm.cu:96); the
 // semantics are those of the CPU oracle's blockwise restatement.
 //
-// Structure (one persistent CTA per SM, 320 threads):
-//   warp 0      TMA producer (as in the dense kernel).
-//   warp 1      MMA issuer: per K block, four tcgen05.mma kind::i8 that OVERWRITE one of two tensor-memory
-//               partial buffers (accumulate disabled on the first), then a commit to that buffer's barrier.
-//   warps 2..9  promotion: tcgen05.ld the int32 partial, convert to fp32, fma with the block's scale into
-//               fp32 register accumulators while the MMA warp already fills the other buffer.  Warp w owns
-//               TMEM lane quarter (w % 4) and column half ((w - 2) / 4) of the tile; a column half never
-//               straddles a 128-wide weight-scale block.  At the end of the tile the same warps cast to
-//               bf16 and store.
+// Structure (one persistent CTA per SM, 640 threads = 5 warpgroups):
+//   warpgroup 0 control: warp 0 TMA producer (as in the dense kernel); warp 1 MMA issuer -- per K block, four
+//               tcgen05.mma kind::i8 that overwrite one of NBUF = 512 / BN tensor-memory partial buffers, then a
+//               commit to that buffer's barrier; warp 2 allocates tensor memory; the group gives most of its
+//               registers back (setmaxnreg.dec).
+//   warps 4..19 promotion (16 warps, setmaxnreg.inc): tcgen05.ld the int32 partial, hand the buffer back to the
+//               MMA warp as soon as the loads have landed in registers, then convert to fp32 and fma with the
+//               block's scale into fp32 register accumulators.  Warp w owns TMEM lane quarter (w % 4) and column
+//               quarter ((w - 4) / 4) of the tile; a column quarter never straddles a 128-wide weight-scale
+//               block.  At the end of the tile the same warps cast to bf16 and store.
+//
+// What bounds it (measured): the hand-over chain commit -> promotion warps wake -> load -> arrive -> MMA thread
+// wakes -> next MMA starts costs about 1000 cycles per K block whatever the arithmetic, against ~750 cycles of
+// tensor-core time per 128 x 256 x 128 block; with B partial buffers the period per K block is
+// max(MMA, (MMA + hand-over + load) / B, promotion issue time), so the buffers are released before the arithmetic
+// and the narrower tile (four buffers) is preferred where its MMA efficiency allows.
 #pragma once
 
 #include "k_dense.cuh"
 
 namespace gi8 {
 
-constexpr int kBlockwiseThreads = 320;
+constexpr int kBlockwiseThreads = 640;
+constexpr int kPromoWarps = 16;
+constexpr int kPromoRegs = 112;   // registers per promotion thread after setmaxnreg.inc
+constexpr int kControlRegs = 32;  // registers per control-warpgroup thread after setmaxnreg.dec
+constexpr int kLaunchRegs = 96;   // registers per thread at launch: 65536 / 640 rounded down to a multiple of 8
+// setmaxnreg.inc can only take what setmaxnreg.dec gave back inside the same CTA (the pool is the CTA's launch
+// allocation); an unbalanced pair blocks in hardware for ever.
+static_assert(kPromoWarps * (kPromoRegs - kLaunchRegs) <= 4 * (kLaunchRegs - kControlRegs), "setmaxnreg pool unbalanced");
 
 // How a promotion warp turns an int32 partial P (|P| <= 128 * 128 * 128 = 2^21) into fp32 and accumulates it.
-// All three produce bit-identical results: fp32(P) is exact, and the packed f32x2 instructions round each
-// half like the scalar ones.
+// All variants produce bit-identical results: fp32(P) is exact in each, and the packed f32x2 instructions round
+// each half like the scalar ones.
 enum Promotion : int {
-    PROMO_MAGIC = 0,     // per element: integer add of 0x4B400000, fp32 subtract of 12582912.0, fma
-    PROMO_MAGIC_X2 = 1,  // same, with add.f32x2 / fma.f32x2 on register pairs (half the fp32 instructions)
-    PROMO_BIAS_X2 = 2,   // the TMEM buffer is pre-filled with 0x4B400000 and the MMA accumulates onto it, so the
-                         // value read back is already the float 12582912 + P: only the packed subtract and fma
-                         // remain; the warp re-fills the buffer (tcgen05.st) before handing it back
+    PROMO_MAGIC = 0,     // integer add of 0x4B400000, fp32 subtract of 12582912.0, fma
+    PROMO_MAGIC_X2 = 1,  // same, with add.f32x2 / fma.f32x2 on register pairs
+    PROMO_I2F = 2,       // cvt.rn.f32.s32, fma
+    PROMO_ABLATE_HANDSHAKE = 3,  // measurement only (wrong results): buffers are handed straight back
+    PROMO_ABLATE_LOAD = 4,       // measurement only (wrong results): tensor-memory loads, no arithmetic
+    PROMO_ABLATE_SCALES = 5,     // measurement only (wrong results): full arithmetic with a constant scale, no scale loads
+    PROMO_ABLATE_MATH = 6,       // measurement only (wrong results): scale loads and tensor-memory loads, no arithmetic
+    PROMO_ABLATE_FMA_ONLY = 7,   // measurement only (wrong results): one fma per element on the raw bits, no conversion
+    PROMO_ABLATE_CVT_ONLY = 8,   // measurement only (wrong results): one cvt per element, folded with xor
 };
 
 constexpr uint32_t kMagicBits = 0x4B400000u;  // fp32 12582912.0 = 1.5 * 2^23: adding an integer |P| < 2^22 to the
 constexpr float kMagicF32 = 12582912.0f;      // bit pattern adds P to the value exactly
+
+struct BlockwiseParams {
+    void* out;        // bf16 [M,N], leading dimension ldo
+    const float* sa;  // [M, KB], row stride ld_sa
+    const float* sw;  // [ceil(N/128), KB], row stride ld_sw
+    uint32_t* status;
+    int64_t ldo, ld_sa, ld_sw;
+    int M, N, K;
+    int tiles_m, tiles_n;
+    int vec_ok;  // out is 16-byte aligned and ldo % 8 == 0
+};
 
 GI8_DEVICE uint64_t pack_f32x2(uint32_t lo_bits, uint32_t hi_bits)
 {
@@ -61,41 +90,17 @@ GI8_DEVICE uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c)
     return r;
 }
 
-// Stores one 32-bit value to N consecutive TMEM columns (N = 8 or 16) of the warp's 32 lanes.
 template <int N>
-GI8_DEVICE void tmem_fill_32x32b(uint32_t taddr, uint32_t v)
+GI8_DEVICE void setmaxnreg_inc()
 {
-    if constexpr (N == 16) {
-        asm volatile(
-            "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
-            "{%1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v)
-            : "memory");
-    } else {
-        static_assert(N == 8, "fill width");
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(v)
-                     : "memory");
-    }
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
 }
 
 template <int N>
-GI8_DEVICE void tmem_ld_chunk(uint32_t taddr, uint32_t (&r)[N])
+GI8_DEVICE void setmaxnreg_dec()
 {
-    if constexpr (N == 16) tmem_ld_32x32b_x16(taddr, r);
-    else tmem_ld_32x32b_x8(taddr, r);
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
-
-GI8_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
-struct BlockwiseParams {
-    void* out;        // bf16 [M,N], leading dimension ldo
-    const float* sa;  // [M, KB], row stride ld_sa
-    const float* sw;  // [ceil(N/128), KB], row stride ld_sw
-    uint32_t* status;
-    int64_t ldo, ld_sa, ld_sw;
-    int M, N, K;
-    int tiles_m, tiles_n;
-    int vec_ok;  // out is 16-byte aligned and ldo % 8 == 0
-};
 
 template <int BN, int STAGES, int PROMO>
 __global__ void __launch_bounds__(kBlockwiseThreads, 1)
@@ -103,13 +108,13 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                       const BlockwiseParams p)
 {
     static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
-    constexpr int CW = BN / 2;  // columns per promotion warp
-    constexpr int kLd = CW > 64 ? 8 : 16;  // columns per tcgen05.ld; two chunks live at a time (register budget)
-    constexpr bool kBias = PROMO == PROMO_BIAS_X2;
+    constexpr int NBUF = 512 / BN;  // partial buffers in tensor memory (2 or 4)
+    constexpr int CW = BN / 4;      // columns per promotion warp (64 or 32)
+    constexpr bool kPacked = PROMO == PROMO_MAGIC_X2;
     constexpr uint32_t kBytesA = kBM * kBK;
     constexpr uint32_t kBytesB = BN * kBK;
     constexpr uint32_t kStageBytes = kBytesA + kBytesB;
-    constexpr uint32_t kTmemCols = 2 * BN;  // 256 or 512
+    constexpr uint32_t kTmemCols = 512;
     constexpr uint32_t kIdesc = make_idesc_i8(kBM, BN, false);
 
     extern __shared__ uint8_t smem_raw[];
@@ -117,8 +122,8 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
     __shared__ __align__(8) uint64_t bar_full[STAGES];
     __shared__ __align__(8) uint64_t bar_empty[STAGES];
-    __shared__ __align__(8) uint64_t bar_part_full[2];
-    __shared__ __align__(8) uint64_t bar_part_empty[2];
+    __shared__ __align__(8) uint64_t bar_part_full[NBUF];
+    __shared__ __align__(8) uint64_t bar_part_empty[NBUF];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
 
@@ -133,15 +138,15 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             mbar_init(&bar_full[s], 1);
             mbar_init(&bar_empty[s], 1);
         }
-        for (int b = 0; b < 2; ++b) {
+        for (int b = 0; b < NBUF; ++b) {
             mbar_init(&bar_part_full[b], 1);
-            mbar_init(&bar_part_empty[b], 8);
+            mbar_init(&bar_part_empty[b], kPromoWarps);
         }
         fence_barrier_init();
         prefetch_tensormap(&map_x);
         prefetch_tensormap(&map_y);
     }
-    if (warp == 1) {
+    if (warp == 2) {
         tmem_alloc(&tmem_base_slot, kTmemCols);
         tmem_relinquish_alloc_permit();
     }
@@ -150,165 +155,197 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
-    if (warp == 0) {
-        // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            uint32_t it = 0;
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                int mb, nb;
-                tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!wait_or_abort(&bar_empty[s], ph ^ 1, &abort_flag)) {
-                        raise_error(p.status, &abort_flag, ERR_TIMEOUT_PRODUCER);
-                        ok = false;
+    if (warp < 4) {
+        setmaxnreg_dec<kControlRegs>();
+        if (warp == 0) {
+            // -------------------------------------------------------------- TMA producer
+            if (lane == 0) {
+                uint32_t it = 0;
+                bool ok = true;
+                for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                    int mb, nb;
+                    tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const uint32_t s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        if (!wait_or_abort(&bar_empty[s], ph ^ 1, &abort_flag)) {
+                            raise_error(p.status, &abort_flag, ERR_TIMEOUT_PRODUCER);
+                            ok = false;
+                            break;
+                        }
+                        uint8_t* sa_tile = smem + s * kStageBytes;
+                        mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
+                        tma_load_2d(sa_tile, &map_x, &bar_full[s], kb * kBK, mb * kBM);
+                        tma_load_2d(sa_tile + kBytesA, &map_y, &bar_full[s], kb * kBK, nb * BN);
+                    }
+                }
+                const uint32_t armed = it < STAGES ? it : STAGES;
+                for (uint32_t j = 0; j < armed; ++j) {
+                    const uint32_t i2 = it - 1 - j;
+                    if (!mbar_wait(&bar_full[i2 % STAGES], (i2 / STAGES) & 1)) {
+                        raise_error(p.status, &abort_flag, ERR_TIMEOUT_DRAIN);
                         break;
                     }
-                    uint8_t* sa_tile = smem + s * kStageBytes;
-                    mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
-                    tma_load_2d(sa_tile, &map_x, &bar_full[s], kb * kBK, mb * kBM);
-                    tma_load_2d(sa_tile + kBytesA, &map_y, &bar_full[s], kb * kBK, nb * BN);
                 }
             }
-            const uint32_t armed = it < STAGES ? it : STAGES;
-            for (uint32_t j = 0; j < armed; ++j) {
-                const uint32_t i2 = it - 1 - j;
-                if (!mbar_wait(&bar_full[i2 % STAGES], (i2 / STAGES) & 1)) {
-                    raise_error(p.status, &abort_flag, ERR_TIMEOUT_DRAIN);
-                    break;
-                }
-            }
-        }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            uint32_t it = 0;  // running K-block counter: selects both the smem stage and the TMEM buffer
-            bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    const uint32_t buf = it & 1;
-                    const uint32_t bph = (it >> 1) & 1;
-                    // kBias: the buffer's first hand-over is the promotion warps' initial fill (one extra phase)
-                    if (!wait_or_abort(&bar_part_empty[buf], kBias ? bph : (bph ^ 1), &abort_flag) ||
-                        !wait_or_abort(&bar_full[s], ph, &abort_flag)) {
-                        raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
-                        ok = false;
-                        break;
-                    }
-                    tcgen05_fence_after_sync();
-                    const uint32_t tmem_d = tmem_base + buf * BN;
-                    const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
-                    const uint64_t da = make_smem_desc_k128(a_addr);
-                    const uint64_t db = make_smem_desc_k128(a_addr + kBytesA);
+        } else if (warp == 1) {
+            // -------------------------------------------------------------- MMA issuer
+            if (lane == 0) {
+                uint32_t it = 0;  // running K-block counter: selects both the smem stage and the TMEM buffer
+                bool ok = true;
+                for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const uint32_t s = it % STAGES;
+                        const uint32_t ph = (it / STAGES) & 1;
+                        const uint32_t buf = it % NBUF;
+                        const uint32_t bph = (it / NBUF) & 1;
+                        if (!wait_or_abort(&bar_part_empty[buf], bph ^ 1, &abort_flag) ||
+                            !wait_or_abort(&bar_full[s], ph, &abort_flag)) {
+                            raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
+                            ok = false;
+                            break;
+                        }
+                        tcgen05_fence_after_sync();
+                        const uint32_t tmem_d = tmem_base + buf * BN;
+                        const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+                        const uint64_t da = make_smem_desc_k128(a_addr);
+                        const uint64_t db = make_smem_desc_k128(a_addr + kBytesA);
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k)
-                        umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kBias || k != 0) ? 1u : 0u);
-                    umma_commit(&bar_empty[s]);
-                    umma_commit(&bar_part_full[buf]);
+                        for (int k = 0; k < kBK / kUmmaK; ++k)
+                            umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, k != 0 ? 1u : 0u);
+                        umma_commit(&bar_empty[s]);
+                        umma_commit(&bar_part_full[buf]);
+                    }
                 }
             }
         }
     } else {
         // ------------------------------------------------------------------ promotion + epilogue warps
+        setmaxnreg_inc<kPromoRegs>();
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int cg = (warp - 4) >> 2;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        uint32_t it = 0;
+        constexpr int kChunk = 16;          // columns per tensor-memory load
+        constexpr int NC = CW / kChunk;     // chunks per K block per warp (4 or 2, even)
+        static_assert(NC % 2 == 0, "the two chunk registers alternate statically");
+        uint32_t it = 0;                    // running K-block counter, as in the MMA warp
         bool ok = true;
 
-        if constexpr (kBias) {
-            // Pre-fill this warp's part of both partial buffers with the magic constant, then hand them over.
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-#pragma unroll
-                for (int c = 0; c < CW; c += kLd) tmem_fill_32x32b<kLd>(tmem_base + lane_base + b * BN + half * CW + c, kMagicBits);
+        // Software pipeline over 16-column chunks that runs ACROSS K blocks: while chunk c is converted and
+        // accumulated, the load of the next chunk -- the first chunk of the next K block when c is the last --
+        // is already in flight, so neither the tensor-memory load latency nor the hand-over to the MMA warp sits
+        // in front of the arithmetic.  A buffer is handed back as soon as its last chunk is in registers.
+        uint32_t va[kChunk], vb[kChunk];
+        const int first_tile = blockIdx.x;
+        if (first_tile < num_tiles) {
+            if (!wait_or_abort(&bar_part_full[0], 0, &abort_flag)) {
+                if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
+                ok = false;
             }
-            tmem_st_wait();
-            tcgen05_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&bar_part_empty[0]);
-                mbar_arrive(&bar_part_empty[1]);
+            ok = __all_sync(0xffffffffu, ok);
+            if (ok) {
+                tcgen05_fence_after_sync();
+                tmem_ld_32x32b_x16(tmem_base + lane_base + cg * CW, va);
+                tmem_ld_wait();
             }
         }
 
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int tile = first_tile; tile < num_tiles && ok; tile += gridDim.x) {
             int mb, nb;
             tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
             const int row = mb * kBM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
-            const int col_base = nb * BN + half * CW;  // first output column of this warp
-            // A column half lies inside one 128-wide weight-scale block (CW divides 128, col_base % CW == 0).
+            const int col_base = nb * BN + cg * CW;  // first output column of this warp
+            // A column quarter lies inside one 128-wide weight-scale block (CW divides 128, col_base % CW == 0).
             const bool cols_ok = col_base < p.N;
             const float* sa_row = p.sa + static_cast<int64_t>(row_ok ? row : 0) * p.ld_sa;
             const float* sw_row = p.sw + static_cast<int64_t>(cols_ok ? col_base / 128 : 0) * p.ld_sw;
+            const bool last_tile = tile + static_cast<int>(gridDim.x) >= num_tiles;
 
-            // fp32 accumulators, two per 64-bit register pair: acc2[j] = {column 2j, column 2j + 1}
-            uint64_t acc2[CW / 2];
+            float acc[CW];
 #pragma unroll
-            for (int j = 0; j < CW / 2; ++j) acc2[j] = 0ull;
+            for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
 
             float sa_next = __ldg(sa_row);
             float sw_next = __ldg(sw_row);
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                const uint32_t buf = it & 1;
-                const uint32_t bph = (it >> 1) & 1;
-                const float t = sa_next * sw_next;  // fp32, round to nearest: the scale of this K block
-                if (kb + 1 < num_kb) {
+                float t = sa_next * sw_next;  // fp32, round to nearest: the scale of this K block
+                if constexpr (PROMO == PROMO_ABLATE_SCALES) t = 0.5f;
+                if (PROMO != PROMO_ABLATE_SCALES && kb + 1 < num_kb) {
                     sa_next = __ldg(sa_row + kb + 1);
                     sw_next = __ldg(sw_row + kb + 1);
                 }
-                const uint64_t t2 = pack_f32x2(__float_as_uint(t), __float_as_uint(t));
-                const uint64_t neg_magic2 = pack_f32x2(__float_as_uint(-kMagicF32), __float_as_uint(-kMagicF32));
-                if (!wait_or_abort(&bar_part_full[buf], bph, &abort_flag)) {
-                    if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
-                    ok = false;
-                    break;
-                }
-                tcgen05_fence_after_sync();
-                const uint32_t taddr = tmem_base + lane_base + buf * BN + half * CW;
+                const uint32_t taddr = tmem_base + lane_base + (it % NBUF) * BN + cg * CW;
 
-                // Software pipeline over 16-column chunks: the load of chunk c + 1 is in flight while chunk c
-                // is converted and accumulated.
-                uint32_t va[kLd], vb[kLd];
-                auto consume = [&](const uint32_t (&v)[kLd], int c) {
+                auto consume = [&](const uint32_t (&v)[kChunk], int c) {
+                    if constexpr (PROMO == PROMO_ABLATE_HANDSHAKE) return;
+                    if constexpr (PROMO == PROMO_ABLATE_LOAD) {
+                        acc[c] = __uint_as_float(__float_as_uint(acc[c]) ^ v[0] ^ v[kChunk - 1]);
+                        return;
+                    }
+                    if constexpr (PROMO == PROMO_ABLATE_MATH) {
+                        acc[c] = __uint_as_float(__float_as_uint(acc[c]) ^ v[0] ^ v[kChunk - 1]) + t;
+                        return;
+                    }
 #pragma unroll
-                    for (int j = 0; j < kLd; j += 2) {
-                        if constexpr (PROMO == PROMO_MAGIC) {
-                            float lo, hi;
-                            unpack_f32x2(acc2[(c + j) / 2], lo, hi);
-                            lo = fmaf(__uint_as_float(v[j] + kMagicBits) - kMagicF32, t, lo);
-                            hi = fmaf(__uint_as_float(v[j + 1] + kMagicBits) - kMagicF32, t, hi);
-                            acc2[(c + j) / 2] = pack_f32x2(__float_as_uint(lo), __float_as_uint(hi));
+                    for (int j = 0; j < kChunk; j += 2) {
+                        if constexpr (PROMO == PROMO_ABLATE_FMA_ONLY) {
+                            acc[c + j] = fmaf(__uint_as_float(v[j]), t, acc[c + j]);
+                            acc[c + j + 1] = fmaf(__uint_as_float(v[j + 1]), t, acc[c + j + 1]);
+                        } else if constexpr (PROMO == PROMO_ABLATE_CVT_ONLY) {
+                            acc[c + j] = __int2float_rn(static_cast<int32_t>(v[j]) + __float_as_int(acc[c + j]));
+                            acc[c + j + 1] = __int2float_rn(static_cast<int32_t>(v[j + 1]) + __float_as_int(acc[c + j + 1]));
+                        } else if constexpr (kPacked) {
+                            const uint64_t neg2 = pack_f32x2(__float_as_uint(-kMagicF32), __float_as_uint(-kMagicF32));
+                            const uint64_t t2 = pack_f32x2(__float_as_uint(t), __float_as_uint(t));
+                            const uint64_t pf = add_f32x2(pack_f32x2(v[j] + kMagicBits, v[j + 1] + kMagicBits), neg2);
+                            const uint64_t a2 = fma_f32x2(
+                                pf, t2, pack_f32x2(__float_as_uint(acc[c + j]), __float_as_uint(acc[c + j + 1])));
+                            unpack_f32x2(a2, acc[c + j], acc[c + j + 1]);
+                        } else if constexpr (PROMO == PROMO_I2F || PROMO == PROMO_ABLATE_SCALES) {
+                            acc[c + j] = fmaf(__int2float_rn(static_cast<int32_t>(v[j])), t, acc[c + j]);
+                            acc[c + j + 1] = fmaf(__int2float_rn(static_cast<int32_t>(v[j + 1])), t, acc[c + j + 1]);
                         } else {
-                            const uint32_t b0 = kBias ? v[j] : v[j] + kMagicBits;
-                            const uint32_t b1 = kBias ? v[j + 1] : v[j + 1] + kMagicBits;
-                            const uint64_t pf = add_f32x2(pack_f32x2(b0, b1), neg_magic2);  // exact fp32(P)
-                            acc2[(c + j) / 2] = fma_f32x2(pf, t2, acc2[(c + j) / 2]);
+                            acc[c + j] = fmaf(__uint_as_float(v[j] + kMagicBits) - kMagicF32, t, acc[c + j]);
+                            acc[c + j + 1] = fmaf(__uint_as_float(v[j + 1] + kMagicBits) - kMagicF32, t, acc[c + j + 1]);
                         }
                     }
                 };
-                tmem_ld_chunk<kLd>(taddr, va);
-                tmem_ld_wait();
+
 #pragma unroll
-                for (int c = 0; c < CW; c += 2 * kLd) {
-                    tmem_ld_chunk<kLd>(taddr + c + kLd, vb);
-                    if constexpr (kBias) tmem_fill_32x32b<kLd>(taddr + c, kMagicBits);
-                    consume(va, c);
-                    tmem_ld_wait();
-                    if (c + 2 * kLd < CW) tmem_ld_chunk<kLd>(taddr + c + 2 * kLd, va);
-                    if constexpr (kBias) tmem_fill_32x32b<kLd>(taddr + c + kLd, kMagicBits);
-                    consume(vb, c + kLd);
-                    if (c + 2 * kLd < CW) tmem_ld_wait();
+                for (int c = 0; c < NC; ++c) {
+                    // Chunk c of this K block is in va (c even) or vb (c odd) and has landed.
+                    bool in_flight = false;
+                    if (c + 1 < NC) {
+                        if (c & 1) tmem_ld_32x32b_x16(taddr + (c + 1) * kChunk, va);
+                        else tmem_ld_32x32b_x16(taddr + (c + 1) * kChunk, vb);
+                        in_flight = true;
+                    } else {
+                        // Last chunk: the whole buffer is in registers -> hand it back, then start on the next
+                        // K block (possibly the next tile's first) before doing this chunk's arithmetic.
+                        tcgen05_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&bar_part_empty[it % NBUF]);
+                        const bool have_next = (kb + 1 < num_kb) || !last_tile;
+                        if (have_next) {
+                            const uint32_t nit = it + 1;
+                            if (!wait_or_abort(&bar_part_full[nit % NBUF], (nit / NBUF) & 1, &abort_flag)) {
+                                if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
+                                ok = false;
+                            }
+                            ok = __all_sync(0xffffffffu, ok);
+                            if (ok) {
+                                tcgen05_fence_after_sync();
+                                tmem_ld_32x32b_x16(tmem_base + lane_base + (nit % NBUF) * BN + cg * CW, va);
+                                in_flight = true;
+                            }
+                        }
+                    }
+                    if (c & 1) consume(vb, c * kChunk);
+                    else consume(va, c * kChunk);
+                    if (in_flight) tmem_ld_wait();
                 }
-                if constexpr (kBias) tmem_st_wait();
-                tcgen05_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_part_empty[buf]);
+                if (!ok) break;
             }
             if (!ok) break;
 
@@ -316,22 +353,14 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col_base;
                 if (col_base + CW <= p.N && p.vec_ok) {
 #pragma unroll
-                    for (int j = 0; j < CW; j += 8) {
-                        float f[8];
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) unpack_f32x2(acc2[j / 2 + q], f[2 * q], f[2 * q + 1]);
+                    for (int j = 0; j < CW; j += 8)
                         *reinterpret_cast<uint4*>(dst + j) =
-                            make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
-                                       pack_bf16x2(f[6], f[7]));
-                    }
+                            make_uint4(pack_bf16x2(acc[j], acc[j + 1]), pack_bf16x2(acc[j + 2], acc[j + 3]),
+                                       pack_bf16x2(acc[j + 4], acc[j + 5]), pack_bf16x2(acc[j + 6], acc[j + 7]));
                 } else {
 #pragma unroll
-                    for (int j = 0; j < CW; j += 2) {
-                        float lo, hi;
-                        unpack_f32x2(acc2[j / 2], lo, hi);
-                        if (col_base + j < p.N) dst[j] = to_bf16_bits(lo);
-                        if (col_base + j + 1 < p.N) dst[j + 1] = to_bf16_bits(hi);
-                    }
+                    for (int j = 0; j < CW; ++j)
+                        if (col_base + j < p.N) dst[j] = to_bf16_bits(acc[j]);
                 }
             }
             __syncwarp();
@@ -340,7 +369,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
     tcgen05_fence_before_sync();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 2) {
         __syncwarp();
         tcgen05_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);

@@ -64,8 +64,8 @@ GI8_DEVICE bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t*
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 0x3f) == 0) {
+        if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
+        if ((++spins & 0xf) == 0) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > GI8_WAIT_LIMIT_NS) return false;
         }

@@ -237,4 +237,228 @@ smallm_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     }
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Cluster variant: the SPLITS CTAs that share one weight tile form a thread-block cluster (1 x SPLITS x 1,
+// SPLITS <= 8).  Each CTA parks its int32 partial tile in its own shared memory; after a cluster barrier,
+// CTA r sums token rows r, r + SPLITS, ... over all peers through distributed shared memory, applies the
+// scales and stores bf16.  No global scratch, no atomics, and the sum is exact whatever the order.
+// The two cluster barriers are hardware barriers that every thread of every CTA reaches unconditionally.
+// ---------------------------------------------------------------------------------------------------
+GI8_DEVICE void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+GI8_DEVICE uint32_t cluster_cta_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// Address of `local_smem_addr` in the shared memory of cluster CTA `rank`.
+GI8_DEVICE uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
+    return r;
+}
+
+GI8_DEVICE int32_t ld_dsmem_s32(uint32_t cluster_addr)
+{
+    int32_t v;
+    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
+    return v;
+}
+
+template <int MT, int STAGES>
+__global__ void __launch_bounds__(kSmallMThreads)
+smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                      const SmallMParams p)
+{
+    static_assert(MT == 16 || MT == 32 || MT == 64 || MT == 128, "token tile must be 16, 32, 64 or 128");
+    constexpr uint32_t kBytesW = kSmallMTileN * kBK;
+    constexpr uint32_t kBytesX = MT * kBK;
+    constexpr uint32_t kBytesXPad = (kBytesX + 1023u) & ~1023u;
+    constexpr uint32_t kStageBytes = kBytesW + kBytesXPad;
+    constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;
+    constexpr uint32_t kIdesc = make_idesc_i8(kSmallMTileN, MT, false);
+    static_assert(STAGES * kStageBytes >= MT * kSmallMTileN * 4, "partial tile must fit in the pipeline buffers");
+
+    extern __shared__ uint8_t smem_raw[];
+    // The dynamic shared window starts at the same offset in every CTA of the cluster, so the aligned base
+    // (and with it the partial tile's address) is identical across peers.
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    __shared__ __align__(8) uint64_t bar_full[STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[STAGES];
+    __shared__ __align__(8) uint64_t bar_acc_full;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile uint32_t abort_flag;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int tile_n = blockIdx.x;
+    const int split = blockIdx.y;            // == rank inside the (1 x SPLITS x 1) cluster
+    const int kb_total = (p.K + kBK - 1) / kBK;
+    const int kb_begin = split * p.kb_per_split;
+    const int kb_end = min(kb_total, kb_begin + p.kb_per_split);
+    const int num_kb = max(0, kb_end - kb_begin);
+
+    if (warp == 0 && lane == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_empty[s], 1);
+        }
+        mbar_init(&bar_acc_full, 1);
+        fence_barrier_init();
+        fence_proxy_async_smem();
+        prefetch_tensormap(&map_w);
+        prefetch_tensormap(&map_x);
+        const uint64_t pol_w = l2_policy_evict_first();
+        const uint64_t pol_x = l2_policy_evict_last();
+        const int first = min(num_kb, STAGES);
+        for (int i = 0; i < first; ++i) {
+            uint8_t* sw_tile = smem + i * kStageBytes;
+            mbar_arrive_expect_tx(&bar_full[i], kBytesW + kBytesX);
+            tma_load_2d_hint(sw_tile, &map_w, &bar_full[i], (kb_begin + i) * kBK, tile_n * kSmallMTileN, pol_w);
+            tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[i], (kb_begin + i) * kBK, 0, pol_x);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_slot, kTmemCols);
+        tmem_relinquish_alloc_permit();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+    int32_t* partial = reinterpret_cast<int32_t*>(smem);  // [MT][128], reuses the pipeline buffers once drained
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint64_t pol_w = l2_policy_evict_first();
+            const uint64_t pol_x = l2_policy_evict_last();
+            int issued = min(num_kb, STAGES);
+            for (int i = STAGES; i < num_kb; ++i) {
+                const uint32_t s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (!wait_or_abort(&bar_empty[s], ph ^ 1, &abort_flag)) {
+                    raise_error(p.status, &abort_flag, ERR_TIMEOUT_PRODUCER);
+                    break;
+                }
+                uint8_t* sw_tile = smem + s * kStageBytes;
+                mbar_arrive_expect_tx(&bar_full[s], kBytesW + kBytesX);
+                tma_load_2d_hint(sw_tile, &map_w, &bar_full[s], (kb_begin + i) * kBK, tile_n * kSmallMTileN, pol_w);
+                tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[s], (kb_begin + i) * kBK, 0, pol_x);
+                issued = i + 1;
+            }
+            const int armed = issued < STAGES ? issued : STAGES;
+            for (int j = 0; j < armed; ++j) {
+                const int i2 = issued - 1 - j;
+                if (!mbar_wait(&bar_full[i2 % STAGES], (i2 / STAGES) & 1)) {
+                    raise_error(p.status, &abort_flag, ERR_TIMEOUT_DRAIN);
+                    break;
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && num_kb > 0) {
+            bool ok = true;
+            for (int i = 0; i < num_kb; ++i) {
+                const uint32_t s = i % STAGES;
+                const uint32_t ph = (i / STAGES) & 1;
+                if (!wait_or_abort(&bar_full[s], ph, &abort_flag)) {
+                    raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after_sync();
+                const uint32_t w_addr = smem_u32(smem + s * kStageBytes);
+                const uint64_t dw = make_smem_desc_k128(w_addr);
+                const uint64_t dx = make_smem_desc_k128(w_addr + kBytesW);
+#pragma unroll
+                for (int k = 0; k < kBK / kUmmaK; ++k) umma_i8(tmem_base, dw + 2 * k, dx + 2 * k, kIdesc, (i | k) != 0);
+                umma_commit(&bar_empty[s]);
+            }
+            if (ok) umma_commit(&bar_acc_full);
+        }
+    } else {
+        // epilogue warps: tensor memory -> this CTA's partial tile in shared memory (or straight to global)
+        const int quarter = warp & 3;
+        const int n_local = quarter * 32 + lane;
+        const int n = tile_n * kSmallMTileN + n_local;
+        bool ok = true;
+        if (num_kb > 0) {
+            // bar_acc_full completes only after every MMA has finished reading the pipeline buffers, so they
+            // can be overwritten with the partial tile from here on.
+            if (!wait_or_abort(&bar_acc_full, 0, &abort_flag)) {
+                if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);  // the tensor-memory loads below are warp-collective
+            tcgen05_fence_after_sync();
+        }
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll
+        for (int c = 0; c < MT; c += 16) {
+            uint32_t t16[16];
+            if (ok && num_kb > 0) {
+                tmem_ld_32x32b_x16(taddr + c, t16);
+                tmem_ld_wait();
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) t16[j] = 0;
+            }
+            if (p.splits == 1) {
+                if (n < p.N) {
+                    const float col_scale = __ldg(p.sw + n);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c + j < p.M) {
+                            const float t = __ldg(p.sx + c + j) * col_scale;
+                            static_cast<uint16_t*>(p.out)[static_cast<int64_t>(c + j) * p.ldo + n] =
+                                to_bf16_bits(__int2float_rn(static_cast<int32_t>(t16[j])) * t);
+                        }
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c + j < p.M) partial[(c + j) * kSmallMTileN + n_local] = static_cast<int32_t>(t16[j]);
+            }
+        }
+    }
+
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (p.splits > 1) {
+        cluster_sync_all();  // every CTA's partial tile is complete and visible cluster-wide
+        if (warp >= 2) {
+            const int n_local = (warp & 3) * 32 + lane;
+            const int n = tile_n * kSmallMTileN + n_local;
+            const uint32_t my_rank = cluster_cta_rank();
+            const uint32_t nranks = static_cast<uint32_t>(p.splits);
+            const float col_scale = n < p.N ? __ldg(p.sw + n) : 0.0f;
+            for (int m = static_cast<int>(my_rank); m < p.M; m += static_cast<int>(nranks)) {
+                const uint32_t local = smem_u32(partial + m * kSmallMTileN + n_local);
+                int32_t total = 0;
+                for (uint32_t r = 0; r < nranks; ++r) total += ld_dsmem_s32(map_to_cta(local, r));
+                if (n < p.N) {
+                    const float t = __ldg(p.sx + m) * col_scale;
+                    static_cast<uint16_t*>(p.out)[static_cast<int64_t>(m) * p.ldo + n] =
+                        to_bf16_bits(__int2float_rn(total) * t);
+                }
+            }
+        }
+        cluster_sync_all();  // nobody exits (and frees its shared memory) while a peer may still read it
+    }
+    if (warp == 1) {
+        __syncwarp();
+        tcgen05_fence_after_sync();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 }  // namespace gi8

@@ -83,6 +83,51 @@ GI8_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity)
     return ok != 0;
 }
 
+// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or about
+// `hint_ns` nanoseconds pass, instead of burning issue slots that working warps on the same scheduler need.
+GI8_DEVICE bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
+// Polls the barrier up to `tries` times in a loop of three instructions per poll (try_wait, branch, counter),
+// with no integer-pipe work besides the counter: the promotion kernels convert on the same half-rate integer pipe
+// that a heavier polling loop would occupy.  Returns true once the phase has completed.
+GI8_DEVICE bool mbar_poll(uint64_t* bar, uint32_t parity, uint32_t tries)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p, q;\n\t"
+        ".reg .u32 n;\n\t"
+        "mov.u32 n, %3;\n\t"
+        "POLL:\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "@p bra.uni DONE;\n\t"
+        "sub.u32 n, n, 1;\n\t"
+        "setp.ne.u32 q, n, 0;\n\t"
+        "@q bra.uni POLL;\n\t"
+        "DONE:\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(tries)
+        : "memory");
+    return ok != 0;
+}
+
+constexpr uint32_t kWaitHintNs = 20000;  // per try_wait; the overall limit below is enforced with %globaltimer
+
 // Wall-clock limit of one wait.  Generous against any legitimate stall (a whole kernel takes
 // milliseconds), short enough that a protocol bug ends the kernel instead of hanging the GPU.
 #ifndef GI8_WAIT_LIMIT_NS
@@ -96,8 +141,8 @@ GI8_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity)
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > GI8_WAIT_LIMIT_NS) return false;
+        if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
+        if ((++spins & 0xf) == 0 && globaltimer_ns() - t0 > GI8_WAIT_LIMIT_NS) return false;
     }
 }
 

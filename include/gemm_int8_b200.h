@@ -63,10 +63,12 @@ int gi8_matmul_i32(const int8_t* x, const int8_t* y, int32_t* out_i32, int64_t M
 /*
  * out[m,n] = bf16( fp32(acc[m,n]) * (sx[m] * sw[n]) ), sx fp32 [M] per-token, sw fp32 [N] per output
  * channel.  No counterpart in the reference (its epilogue takes one scalar, gemm.cu:96).
- * Small-M shapes run a split-K weight-streaming kernel that needs scratch: `workspace` must hold at
- * least gi8_matmul_scaled_workspace_bytes(M,N,K) bytes, 16-byte aligned, AND BE ZERO-FILLED before
- * the first call; the kernel leaves it zero-filled again on completion, so one zeroed buffer can be
- * reused by successive calls on the same stream.  Pass NULL/0 when that function returns 0.
+ * Small-M shapes (M <= 64) run a split-K weight-streaming kernel.  By default its K slices are reduced
+ * inside a thread-block cluster and no scratch is needed (gi8_matmul_scaled_workspace_bytes returns 0).
+ * The "smallm" variant reduces through global scratch instead: `workspace` must then hold at least
+ * gi8_matmul_scaled_workspace_bytes(M,N,K) bytes, 16-byte aligned, AND BE ZERO-FILLED before the first
+ * call; the kernel leaves it zero-filled again on completion, so one zeroed buffer can be reused by
+ * successive calls on the same stream.  Pass NULL/0 when that function returns 0.
  */
 int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out_bf16,
                       int64_t M, int64_t N, int64_t K, void* workspace, int64_t workspace_bytes, void* stream);
@@ -113,7 +115,8 @@ int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, 
 /*
  * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted
  * per-shape dispatch that replaces the reference's shape table (csrc/kernels/gemm.cu:136-161).
- * Names: "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "auto".  Returns GI8_ERR_INVALID_ARGUMENT
+ * Names: "dense_bn256", "dense_bn128", "dense_bn64", "smallm" (split-K through global scratch),
+ * "smallm_cluster" (split-K through distributed shared memory), "auto".  Returns GI8_ERR_INVALID_ARGUMENT
  * for an unknown name.
  */
 int gi8_force_variant(const char* name);

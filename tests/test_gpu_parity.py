@@ -158,7 +158,7 @@ def test_reference_benchmark_shapes(g, oracle):
 
 
 # ---------------------------------------------------------------------------------------- scaled (per token x per channel)
-@pytest.mark.parametrize("variant", DENSE_VARIANTS + ["smallm", None])
+@pytest.mark.parametrize("variant", DENSE_VARIANTS + ["smallm", "smallm_cluster", None])
 def test_scaled_edge_shapes(g, oracle, variant):
     g.force_variant(variant)
     gen = torch.Generator().manual_seed(41)
@@ -178,9 +178,13 @@ def test_config3_decode_shapes(g, oracle, K, N):
 
     for M in (1, 4, 16, 64):
         xq, wq, sx, sw = workloads.decode(M, N, K)
-        assert g.pick_variant(1, M, N, K) == "smallm"
-        out = g.matmul_scaled(xq.cuda(), wq.cuda(), sx.cuda(), sw.cuda())
-        assert_bits_equal(oracle, out, oracle.c_matmul_scaled(xq, wq, sx, sw), f"decode M={M} N={N} K={K}")
+        assert g.pick_variant(1, M, N, K) == "smallm_cluster"
+        ref = oracle.c_matmul_scaled(xq, wq, sx, sw)
+        for variant in (None, "smallm"):     # cluster reduction (default) and global-scratch reduction
+            g.force_variant(variant)
+            out = g.matmul_scaled(xq.cuda(), wq.cuda(), sx.cuda(), sw.cuda())
+            assert_bits_equal(oracle, out, ref, f"decode {variant} M={M} N={N} K={K}")
+        g.force_variant(None)
 
 
 def test_smallm_split_k_scratch_is_left_zeroed(g, oracle):
@@ -192,6 +196,7 @@ def test_smallm_split_k_scratch_is_left_zeroed(g, oracle):
     y[1::2] = 127
     sx, sw = torch.rand(M) + 0.5, torch.rand(N) + 0.5
     xd, yd, sxd, swd = x.cuda(), y.cuda(), sx.cuda(), sw.cuda()
+    g.force_variant("smallm")
     nbytes = int(g._C.gi8_matmul_scaled_workspace_bytes(M, N, K))
     assert nbytes > 0
     ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
@@ -210,6 +215,10 @@ def test_smallm_split_k_scratch_is_left_zeroed(g, oracle):
                                 ctypes.c_void_p(sxd.data_ptr()), ctypes.c_void_p(swd.data_ptr()),
                                 ctypes.c_void_p(out.data_ptr()), M, N, K, ctypes.c_void_p(ws.data_ptr()), 16, stream)
     assert rc == 6
+    g.force_variant(None)
+    assert int(g._C.gi8_matmul_scaled_workspace_bytes(M, N, K)) == 0   # the default (cluster) path needs none
+    out = g.matmul_scaled(xd, yd, sxd, swd)
+    assert_bits_equal(oracle, out, ref, "cluster split-K, extreme values")
 
 
 # ---------------------------------------------------------------------------------------- blockwise

@@ -41,7 +41,7 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
     import gemm_int8_b200 as g
 
     C = g._C
-    g.force_variant(None)
+    g.force_variant("smallm")    # the comparison entry point then runs the same split-K kernel with caller scratch
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
@@ -60,6 +60,7 @@ def test_static_scratch_entry_matches_workspace_entry_twice():
         again = _call_static(C, x, y, sx, sw, stream)       # same inputs, straight after
         torch.cuda.synchronize()
         assert torch.equal(again.view(torch.int16), expect.view(torch.int16))
+    g.force_variant(None)
     assert g.device_status() == 0
 
 
