@@ -276,5 +276,12 @@ def device_status() -> int:
     return int(code.value)
 
 
+# GEMM_INT8_KERNEL=<variant> forces a kernel variant for the whole process (tuning and profiling).
+import os as _os
+
+if _os.environ.get("GEMM_INT8_KERNEL"):
+    force_variant(_os.environ["GEMM_INT8_KERNEL"])
+
+
 __all__ = ["matmul", "matmul_i32", "matmul_scaled", "matmul_blockwise", "force_variant", "pick_variant",
            "device_status"]

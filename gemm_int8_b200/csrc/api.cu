@@ -12,6 +12,7 @@
 #include <mutex>
 
 #include "k_blockwise.cuh"
+#include "k_blockwise2.cuh"
 #include "k_dense.cuh"
 #include "k_smallm.cuh"
 
@@ -42,9 +43,9 @@ int fail(int code, const char* fmt, ...)
 // Kernel status word: one instance per device (module-scope device variable).
 __device__ uint32_t g_kernel_status;
 
-enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM, VAR_SMALLM_CLUSTER };
-const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "smallm_cluster"};
-constexpr int kNumVariants = 6;
+enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM, VAR_SMALLM_CLUSTER, VAR_PAIR };
+const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "smallm_cluster", "pair"};
+constexpr int kNumVariants = 7;
 int g_forced_variant = VAR_AUTO;
 
 struct DeviceState {
@@ -146,6 +147,21 @@ int pick_bn(int64_t M, int64_t N, int sms, bool allow64)
     return best;
 }
 
+// Rasterisation band height in row-blocks: the band's slice of x (group_m x 128 x K bytes) is kept near 16 MB so
+// that it stays in L2 while the band sweeps over y (fitted on 8192^3, 16384^3 and the K = 4096 layer shapes).
+// GEMM_INT8_GROUP_M overrides it for tuning.
+int pick_group_m(int64_t K)
+{
+    if (const char* e = getenv("GEMM_INT8_GROUP_M")) {
+        const int v = atoi(e);
+        if (v >= 1 && v <= 64) return v;
+    }
+    int64_t g = (16ll << 20) / (kBM * (K > 0 ? K : 1));
+    if (g < 4) g = 4;
+    if (g > 32) g = 32;
+    return static_cast<int>(g);
+}
+
 template <typename Kernel>
 int ensure_smem(DeviceState* st, int slot, Kernel kernel, size_t bytes)
 {
@@ -167,6 +183,7 @@ int launch_dense(DeviceState* st, int slot, const int8_t* x, const int8_t* y, De
     if (int rc = make_operand_map(&my, y, p.N, p.K, BN)) return rc;
     p.tiles_m = (p.M + kBM - 1) / kBM;
     p.tiles_n = (p.N + BN - 1) / BN;
+    p.group_m = pick_group_m(p.K);
     const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
     kernel<<<grid, kDenseThreads, smem, stream>>>(mx, my, p);
@@ -205,9 +222,10 @@ int zero_output(void* out, int64_t bytes, cudaStream_t stream)
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Small-M plan: token tile MT, number of K splits and pipeline depth.  Two CTAs fit one SM (about 100 KB
-// of shared memory each), so the split count is chosen to fill 2 x SMs CTA slots without starting a
-// second partial wave, while every split keeps at least two K blocks.
+// Small-M plan: token tile MT, number of K splits and pipeline depth.  Fitted on B200 with device-timed CUDA-graph
+// replays over HBM-cold weights (M in {1,16,64} x {4096x4096, 14336x4096, 4096x14336}): few weight tiles want the
+// largest cluster (8 splits: 32 tiles -> 256 CTAs), many weight tiles want one or two; for M >= 16 the reduction
+// costs more than a second split gains.  Two CTAs fit one SM (about 100 KB of shared memory each).
 // ---------------------------------------------------------------------------------------------------
 struct SmallMPlan {
     bool use;
@@ -228,8 +246,13 @@ SmallMPlan plan_smallm(int64_t M, int64_t N, int64_t K, int sms, bool forced, in
     const int slots = 2 * sms;
     int splits = slots / pl.tiles_n;
     if (splits < 1) splits = 1;
+    if (splits <= 2 && M >= 16) splits = 1;
     if (splits > kb_total / 2) splits = kb_total / 2 > 0 ? kb_total / 2 : 1;
     if (splits > max_splits) splits = max_splits;
+    if (const char* e = getenv("GEMM_INT8_SPLITS")) {  // tuning override
+        const int v = atoi(e);
+        if (v >= 1 && v <= max_splits && v <= kb_total) splits = v;
+    }
     pl.kb_per_split = (kb_total + splits - 1) / splits;
     pl.splits = (kb_total + pl.kb_per_split - 1) / pl.kb_per_split;
     pl.scratch_bytes = pl.splits > 1 ? static_cast<int64_t>(pl.tiles_n) * pl.mt * kSmallMTileN * 4 : 0;
@@ -310,6 +333,19 @@ int get_static_scratch(void** out)
 }  // namespace
 
 extern "C" {
+
+#ifdef GI8_ENABLE_ABLATIONS
+// Tuning builds only (not declared in the public header): copies out and clears the pair kernel's wait counters.
+int gi8_debug_pair_counters(unsigned long long* out, int n)
+{
+    if (n > 148 * 8) n = 148 * 8;
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    if (cudaMemcpyFromSymbol(out, gi8::g_pair_dbg, sizeof(unsigned long long) * n) != cudaSuccess) return 1;
+    static unsigned long long zeros[148 * 8] = {};
+    if (cudaMemcpyToSymbol(gi8::g_pair_dbg, zeros, sizeof(zeros)) != cudaSuccess) return 1;
+    return 0;
+}
+#endif
 
 int gi8_version(void) { return 100; }
 
@@ -505,16 +541,43 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     p.out = out, p.sa = sa, p.sw = sw, p.status = st->status, p.ldo = N, p.ld_sa = ld_sa, p.ld_sw = ld_sw;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
+    CUtensorMap mx, my;
+    if (int rc = make_operand_map(&mx, x, M, K, kBM)) return rc;
+    if (g_forced_variant == VAR_PAIR) {
+        // Two-CTA form: 256 x 128 tiles, one CTA pair per tile.
+        if (int rc = make_operand_map(&my, y, N, K, 64)) return rc;
+        p.tiles_m = (int)((M + kPairBM - 1) / kPairBM);
+        p.tiles_n = (int)((N + 127) / 128);
+        p.group_m = pick_group_m(p.K) / 2 > 0 ? pick_group_m(p.K) / 2 : 1;
+        const int64_t tiles2 = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+        const int pairs = static_cast<int>(tiles2 < st->sm_count / 2 ? tiles2 : st->sm_count / 2);
+        constexpr size_t smem2 = 8 * (kBM + 64) * kBK + 1024;
+        auto kernel2 = blockwise_pair_kernel<8, PROMO_I2F>;
+        if (int rc = ensure_smem(st, 23, kernel2, smem2)) return rc;
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(2 * pairs, 1, 1);
+        cfg.blockDim = dim3(kBlockwiseThreads, 1, 1);
+        cfg.dynamicSmemBytes = smem2;
+        cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel2, mx, my, p));
+        return GI8_OK;
+    }
     int bn;
     switch (g_forced_variant) {
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
         default: bn = pick_bn(M, N, st->sm_count, false);
     }
-    CUtensorMap mx, my;
-    if (int rc = make_operand_map(&mx, x, M, K, kBM)) return rc;
     p.tiles_m = (int)((M + kBM - 1) / kBM);
     p.tiles_n = (int)((N + bn - 1) / bn);
+    p.group_m = pick_group_m(p.K);
     const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
     // Tuning knob (not part of the ABI): GEMM_INT8_PROMOTION = 0 | 1 | 2 selects the promotion arithmetic

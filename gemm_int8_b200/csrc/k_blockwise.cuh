@@ -62,6 +62,7 @@ struct BlockwiseParams {
     int M, N, K;
     int tiles_m, tiles_n;
     int vec_ok;  // out is 16-byte aligned and ldo % 8 == 0
+    int group_m; // row-blocks per rasterisation band
 };
 
 GI8_DEVICE uint64_t pack_f32x2(uint32_t lo_bits, uint32_t hi_bits)
@@ -164,7 +165,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 bool ok = true;
                 for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                     int mb, nb;
-                    tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+                    tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
                     for (int kb = 0; kb < num_kb; ++kb, ++it) {
                         const uint32_t s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
@@ -252,7 +253,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
         for (int tile = first_tile; tile < num_tiles && ok; tile += gridDim.x) {
             int mb, nb;
-            tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+            tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
             const int row = mb * kBM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
             const int col_base = nb * BN + cg * CW;  // first output column of this warp

@@ -47,6 +47,7 @@ struct DenseParams {
     int M, N, K;
     int tiles_m, tiles_n;
     int vec_ok;           // out is 16-byte aligned and ldo keeps every row 16-byte aligned
+    int group_m;          // row-blocks per rasterisation band
     float alpha;
 };
 
@@ -64,8 +65,8 @@ GI8_DEVICE bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t*
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
-        if ((++spins & 0xf) == 0) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 0x3f) == 0) {
             if (*abort_flag) return false;
             if (globaltimer_ns() - t0 > GI8_WAIT_LIMIT_NS) return false;
         }
@@ -74,9 +75,8 @@ GI8_DEVICE bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t*
 
 // Maps a linear tile index to (m block, n block).  Tiles are walked in bands of kGroupM row-blocks so
 // that the tiles resident at one time share X rows and Y rows in L2.
-GI8_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb)
+GI8_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb, int kGroupM = 8)
 {
-    constexpr int kGroupM = 8;
     const int per_group = kGroupM * tiles_n;
     const int g = tile / per_group;
     const int first_m = g * kGroupM;
@@ -145,7 +145,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             bool ok = true;
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
                 int mb, nb;
-                tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+                tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const uint32_t s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
@@ -215,7 +215,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
             int mb, nb;
-            tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+            tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
             const uint32_t buf = local_tile & 1;
             const uint32_t acc_ph = (local_tile >> 1) & 1;
             if (!wait_or_abort(&bar_acc_full[buf], acc_ph, &abort_flag)) {

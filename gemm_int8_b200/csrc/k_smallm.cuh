@@ -64,9 +64,12 @@ smallm_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int tile_n = blockIdx.x;
     const int split = blockIdx.y;
     const int kb_total = (p.K + kBK - 1) / kBK;
-    const int kb_begin = split * p.kb_per_split;
-    const int kb_end = min(kb_total, kb_begin + p.kb_per_split);
-    const int num_kb = max(0, kb_end - kb_begin);
+    // K blocks are dealt round-robin to the splits (split s takes blocks s, s + splits, ...): at any moment the
+    // CTAs that share a weight tile stream ADJACENT 128-byte pieces of every weight row, so the DRAM requests in
+    // flight form runs of splits x STAGES x 128 contiguous bytes per row instead of isolated 128-byte pieces.
+    const int kb_begin = split;
+    const int kb_step = p.splits;
+    const int num_kb = split < kb_total ? (kb_total - split + p.splits - 1) / p.splits : 0;
 
     if (warp == 0 && lane == 0) {
         // The producer thread initialises the barriers itself and starts the first loads before the rest of
@@ -87,8 +90,8 @@ smallm_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int i = 0; i < first; ++i) {
             uint8_t* sw_tile = smem + i * kStageBytes;
             mbar_arrive_expect_tx(&bar_full[i], kBytesW + kBytesX);
-            tma_load_2d_hint(sw_tile, &map_w, &bar_full[i], (kb_begin + i) * kBK, tile_n * kSmallMTileN, pol_w);
-            tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[i], (kb_begin + i) * kBK, 0, pol_x);
+            tma_load_2d_hint(sw_tile, &map_w, &bar_full[i], (kb_begin + i * kb_step) * kBK, tile_n * kSmallMTileN, pol_w);
+            tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[i], (kb_begin + i * kb_step) * kBK, 0, pol_x);
         }
     }
     if (warp == 1) {
@@ -115,8 +118,8 @@ smallm_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 }
                 uint8_t* sw_tile = smem + s * kStageBytes;
                 mbar_arrive_expect_tx(&bar_full[s], kBytesW + kBytesX);
-                tma_load_2d_hint(sw_tile, &map_w, &bar_full[s], (kb_begin + i) * kBK, tile_n * kSmallMTileN, pol_w);
-                tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[s], (kb_begin + i) * kBK, 0, pol_x);
+                tma_load_2d_hint(sw_tile, &map_w, &bar_full[s], (kb_begin + i * kb_step) * kBK, tile_n * kSmallMTileN, pol_w);
+                tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[s], (kb_begin + i * kb_step) * kBK, 0, pol_x);
                 issued = i + 1;
             }
             const int armed = issued < STAGES ? issued : STAGES;
@@ -302,9 +305,12 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     const int tile_n = blockIdx.x;
     const int split = blockIdx.y;            // == rank inside the (1 x SPLITS x 1) cluster
     const int kb_total = (p.K + kBK - 1) / kBK;
-    const int kb_begin = split * p.kb_per_split;
-    const int kb_end = min(kb_total, kb_begin + p.kb_per_split);
-    const int num_kb = max(0, kb_end - kb_begin);
+    // K blocks are dealt round-robin to the splits (split s takes blocks s, s + splits, ...): at any moment the
+    // CTAs that share a weight tile stream ADJACENT 128-byte pieces of every weight row, so the DRAM requests in
+    // flight form runs of splits x STAGES x 128 contiguous bytes per row instead of isolated 128-byte pieces.
+    const int kb_begin = split;
+    const int kb_step = p.splits;
+    const int num_kb = split < kb_total ? (kb_total - split + p.splits - 1) / p.splits : 0;
 
     if (warp == 0 && lane == 0) {
         abort_flag = 0;
@@ -323,8 +329,8 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         for (int i = 0; i < first; ++i) {
             uint8_t* sw_tile = smem + i * kStageBytes;
             mbar_arrive_expect_tx(&bar_full[i], kBytesW + kBytesX);
-            tma_load_2d_hint(sw_tile, &map_w, &bar_full[i], (kb_begin + i) * kBK, tile_n * kSmallMTileN, pol_w);
-            tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[i], (kb_begin + i) * kBK, 0, pol_x);
+            tma_load_2d_hint(sw_tile, &map_w, &bar_full[i], (kb_begin + i * kb_step) * kBK, tile_n * kSmallMTileN, pol_w);
+            tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[i], (kb_begin + i * kb_step) * kBK, 0, pol_x);
         }
     }
     if (warp == 1) {
@@ -351,8 +357,8 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                 }
                 uint8_t* sw_tile = smem + s * kStageBytes;
                 mbar_arrive_expect_tx(&bar_full[s], kBytesW + kBytesX);
-                tma_load_2d_hint(sw_tile, &map_w, &bar_full[s], (kb_begin + i) * kBK, tile_n * kSmallMTileN, pol_w);
-                tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[s], (kb_begin + i) * kBK, 0, pol_x);
+                tma_load_2d_hint(sw_tile, &map_w, &bar_full[s], (kb_begin + i * kb_step) * kBK, tile_n * kSmallMTileN, pol_w);
+                tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[s], (kb_begin + i * kb_step) * kBK, 0, pol_x);
                 issued = i + 1;
             }
             const int armed = issued < STAGES ? issued : STAGES;

@@ -141,8 +141,8 @@ GI8_DEVICE bool mbar_wait(uint64_t* bar, uint32_t parity)
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return true;
-        if ((++spins & 0xf) == 0 && globaltimer_ns() - t0 > GI8_WAIT_LIMIT_NS) return false;
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > GI8_WAIT_LIMIT_NS) return false;
     }
 }
 

@@ -108,7 +108,7 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
  *     overlap (different streams, or different host threads on different streams) race on it -- serialise
  *     them on one stream or with events.
  */
-#define GI8_STATIC_SCRATCH_BYTES (8 * 1024 * 1024)
+#define GI8_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
 int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out_bf16,
                              int64_t M, int64_t N, int64_t K, void* stream);
 
@@ -116,7 +116,8 @@ int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, 
  * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted
  * per-shape dispatch that replaces the reference's shape table (csrc/kernels/gemm.cu:136-161).
  * Names: "dense_bn256", "dense_bn128", "dense_bn64", "smallm" (split-K through global scratch),
- * "smallm_cluster" (split-K through distributed shared memory), "auto".  Returns GI8_ERR_INVALID_ARGUMENT
+ * "smallm_cluster" (split-K through distributed shared memory), "pair" (blockwise GEMM on two-CTA 256 x 128
+ * tiles, tcgen05.mma.cta_group::2), "auto".  Returns GI8_ERR_INVALID_ARGUMENT
  * for an unknown name.
  */
 int gi8_force_variant(const char* name);

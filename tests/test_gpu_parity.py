@@ -222,7 +222,7 @@ def test_smallm_split_k_scratch_is_left_zeroed(g, oracle):
 
 
 # ---------------------------------------------------------------------------------------- blockwise
-@pytest.mark.parametrize("variant", ["dense_bn128", "dense_bn256", None])
+@pytest.mark.parametrize("variant", ["dense_bn128", "dense_bn256", "pair", None])
 def test_blockwise_edge_shapes(g, oracle, variant):
     g.force_variant(variant)
     gen = torch.Generator().manual_seed(51)
@@ -245,7 +245,7 @@ def test_blockwise_promotion_modes_agree(g, oracle, promotion, monkeypatch):
     """The three promotion arithmetics (scalar magic-number, packed, TMEM-biased packed) are bit-identical."""
     monkeypatch.setenv("GEMM_INT8_PROMOTION", promotion)
     gen = torch.Generator().manual_seed(52)
-    for variant in ("dense_bn128", "dense_bn256"):
+    for variant in ("dense_bn128", "dense_bn256", "pair"):
         g.force_variant(variant)
         for (M, N, K) in [(130, 264, 400), (300, 1000, 2048)]:
             KB, NB = -(-K // 128), -(-N // 128)

@@ -70,9 +70,9 @@ def test_static_scratch_entry_rejects_what_does_not_fit():
     C = g._C
     dev = torch.device("cuda", 0)
     stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-    # M = 100 -> token tile 128; N = 18000 -> 141 weight tiles, split in two over K:
-    # 141 * 128 * 512 bytes = 9.2 MB of scratch > 8 MiB
-    M, big_n, K = 100, 18000, 512
+    # M = 100 -> token tile 128; N = 12544 -> 98 weight tiles, split in two over K:
+    # 98 * 128 * 512 bytes = 6.4 MB of scratch > 4 MiB
+    M, big_n, K = 100, 12544, 512
     x = torch.zeros((M, K), dtype=torch.int8, device=dev)
     y = torch.zeros((big_n, K), dtype=torch.int8, device=dev)
     sx = torch.ones(M, device=dev)
