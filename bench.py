@@ -37,6 +37,14 @@ if ROOT not in sys.path:
 METRIC = "INT8 TOPS per shape (fraction of B200 INT8 peak); speedup vs cuBLAS BF16"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under
+# profiles/: keyed by (workload, M, N, K).  Other shapes report null.
+NCU_TRAFFIC = {
+    ("blockwise_prefill", 2048, 11008, 4096): (62.0e6, "profiles/blockwise_gemm_kernel__blockwise_prefill_2048x11008x4096.md"),
+    ("square8192", 8192, 8192, 8192): (444.3e6, "profiles/dense_gemm_kernel__square8192.md"),
+    ("decode", 16, 14336, 4096): (58.97e6, "profiles/smallm_cluster_kernel__decode_16x14336x4096.md"),
+}
+
 WORKLOADS = {
     # name: (M, N, K, kind)
     "blockwise_prefill": (2048, 11008, 4096, "blockwise"),
@@ -417,6 +425,9 @@ def main():
                         "frac": achieved / int8_peak, "traffic": None,
                         "note": f"int8 TOP/s of the GEMM launch; peak = 2 x {peak_kind} bf16 burst "
                                 f"({peaks['bf16_tflops']} TFLOP/s) of {peak_kind}; min step {min(times):.4f} ms"}
+        if (name, M, N, K) in NCU_TRAFFIC and world == 1:
+            roofline["traffic"], roofline["traffic_source"] = NCU_TRAFFIC[(name, M, N, K)]
+            roofline["algorithmic_bytes"] = algo_bytes
         line = {
             "metric": METRIC, "value": tops, "unit": "TOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,

@@ -35,6 +35,8 @@ _libdef.define("int8_matmul(Tensor A, Tensor B, float alpha) -> Tensor")
 _libdef.define("int8_matmul_i32(Tensor A, Tensor B) -> Tensor")
 _libdef.define("int8_matmul_scaled(Tensor A, Tensor B, Tensor a_scale, Tensor b_scale) -> Tensor")
 _libdef.define("int8_matmul_blockwise(Tensor A, Tensor B, Tensor A_scale, Tensor B_scale) -> Tensor")
+_libdef.define("quantize_token_block(Tensor a) -> (Tensor, Tensor)")
+_libdef.define("quantize_token(Tensor a) -> (Tensor, Tensor)")
 
 
 def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
@@ -259,6 +261,55 @@ def matmul_blockwise(x_q: torch.Tensor, w_q: torch.Tensor, x_scale: torch.Tensor
     return torch.ops.gemm_int8_CUDA.int8_matmul_blockwise(x_q, w_q, x_scale, w_scale)
 
 
+def _quantize(a: torch.Tensor, per_block: bool):
+    if not a.is_cuda:
+        raise RuntimeError("quantize: input must be a CUDA tensor (the torch reference lives in gemm_int8_b200.quant)")
+    if a.dim() != 2:
+        raise RuntimeError("quantize: input must be 2-D [tokens, features]")
+    if a.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError(f"quantize: input must be float32 or bfloat16, got {a.dtype}")
+    a = a.contiguous()
+    M, K = a.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=a.device)
+    s = torch.empty((M, -(-K // KBLOCK)) if per_block else (M,), dtype=torch.float32, device=a.device)
+    fn = _C.gi8_quantize_token_block if per_block else _C.gi8_quantize_token
+    with _on_device(a.device):
+        rc = fn(_ptr(a), 0 if a.dtype == torch.float32 else 1, _ptr(q), _ptr(s), M, K, _stream_ptr(a.device))
+    _lib.check(_C, rc)
+    return q, s
+
+
+_libdef.impl("quantize_token_block", lambda a: _quantize(a, True), "CUDA")
+_libdef.impl("quantize_token", lambda a: _quantize(a, False), "CUDA")
+
+
+@torch.library.register_fake(f"{_NS}::quantize_token_block")
+def _(a: torch.Tensor):
+    torch._check(len(a.shape) == 2, lambda: "a must be a 2D tensor")
+    kb = (a.shape[1] + KBLOCK - 1) // KBLOCK
+    return (torch.empty(a.shape[0], a.shape[1], device=a.device, dtype=torch.int8),
+            torch.empty(a.shape[0], kb, device=a.device, dtype=torch.float32))
+
+
+@torch.library.register_fake(f"{_NS}::quantize_token")
+def _(a: torch.Tensor):
+    torch._check(len(a.shape) == 2, lambda: "a must be a 2D tensor")
+    return (torch.empty(a.shape[0], a.shape[1], device=a.device, dtype=torch.int8),
+            torch.empty(a.shape[0], device=a.device, dtype=torch.float32))
+
+
+def quantize_per_token_block(a: torch.Tensor):
+    """Fused activation quantiser for `matmul_blockwise`: a [M, K] fp32/bf16 (CUDA) -> (q int8 [M, K],
+    scales fp32 [M, ceil(K/128)]), one symmetric scale per token per 128-wide K block (amax / 127, round half
+    even, clamp to +-127) -- bit-identical to `quant.quantize_per_token_block`."""
+    return torch.ops.gemm_int8_CUDA.quantize_token_block(a)
+
+
+def quantize_per_token(a: torch.Tensor):
+    """Fused per-token quantiser for `matmul_scaled`: a [M, K] -> (q int8 [M, K], scales fp32 [M])."""
+    return torch.ops.gemm_int8_CUDA.quantize_token(a)
+
+
 def force_variant(name: str | None) -> None:
     """Force a kernel variant ("dense_bn256", "dense_bn128", "dense_bn64", "smallm"); None = fitted dispatch."""
     _lib.check(_C, _C.gi8_force_variant(name.encode() if name else None))
@@ -283,5 +334,7 @@ if _os.environ.get("GEMM_INT8_KERNEL"):
     force_variant(_os.environ["GEMM_INT8_KERNEL"])
 
 
-__all__ = ["matmul", "matmul_i32", "matmul_scaled", "matmul_blockwise", "force_variant", "pick_variant",
-           "device_status"]
+from .linear import Int8Linear  # noqa: E402
+
+__all__ = ["matmul", "matmul_i32", "matmul_scaled", "matmul_blockwise", "quantize_per_token_block",
+           "quantize_per_token", "Int8Linear", "force_variant", "pick_variant", "device_status"]

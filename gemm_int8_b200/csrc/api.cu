@@ -14,6 +14,7 @@
 #include "k_blockwise.cuh"
 #include "k_blockwise2.cuh"
 #include "k_dense.cuh"
+#include "k_quant.cuh"
 #include "k_smallm.cuh"
 
 namespace {
@@ -295,13 +296,18 @@ int launch_smallm_cluster(DeviceState* st, int slot, const int8_t* x, const int8
     cfg.blockDim = dim3(kSmallMThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = pl.splits;
     attr[0].val.clusterDim.z = 1;
+    // Programmatic dependent launch: this kernel's set-up overlaps the tail of the previous kernel in the stream
+    // (it waits with griddepcontrol.wait before its first global access).  GEMM_INT8_PDL=0 turns it off.
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    const char* pdl = getenv("GEMM_INT8_PDL");
+    cfg.numAttrs = (pdl && pdl[0] == '0') ? 1 : 2;
     GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, p));
     return GI8_OK;
 }
@@ -519,6 +525,63 @@ int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, 
         case 64: return launch_smallm<64, 4>(st, 26, x, y, q, pl, s);
         default: return launch_smallm<128, 3>(st, 27, x, y, q, pl, s);
     }
+}
+
+static int check_quant(const void* in, int in_dtype, const int8_t* q, const float* scales, int64_t M, int64_t K)
+{
+    if (M < 0 || K < 0) return fail(GI8_ERR_INVALID_ARGUMENT, "negative dimension");
+    if (in_dtype != 0 && in_dtype != 1) return fail(GI8_ERR_INVALID_ARGUMENT, "in_dtype must be 0 (fp32) or 1 (bf16)");
+    if (M == 0 || K == 0) return GI8_OK;
+    if (!in || !q || !scales) return fail(GI8_ERR_INVALID_ARGUMENT, "null pointer");
+    if (M > INT32_MAX || K > INT32_MAX - 1024) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "dimension too large");
+    const int64_t mult = in_dtype == 0 ? 4 : 8;
+    if (K % mult) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "K=%lld must be a multiple of %lld for this input type",
+                              (long long)K, (long long)mult);
+    if (reinterpret_cast<uintptr_t>(in) % 16 || reinterpret_cast<uintptr_t>(q) % 4 || reinterpret_cast<uintptr_t>(scales) % 4)
+        return fail(GI8_ERR_MISALIGNED, "in must be 16-byte aligned, q and scales 4-byte aligned");
+    return GI8_OK;
+}
+
+int gi8_quantize_token_block(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K, void* stream)
+{
+    if (int rc = check_quant(in, in_dtype, q, scales, M, K)) return rc;
+    if (M == 0 || K == 0) return GI8_OK;
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int KB = static_cast<int>((K + 127) / 128);
+    const int64_t warps = M * KB;
+    int64_t blocks = (warps + kQuantThreads / 32 - 1) / (kQuantThreads / 32);
+    const int64_t cap = static_cast<int64_t>(st->sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    if (in_dtype == 0)
+        quantize_token_block_kernel<float><<<static_cast<int>(blocks), kQuantThreads, 0, s>>>(
+            static_cast<const float*>(in), q, scales, M, static_cast<int>(K), KB);
+    else
+        quantize_token_block_kernel<__nv_bfloat16><<<static_cast<int>(blocks), kQuantThreads, 0, s>>>(
+            static_cast<const __nv_bfloat16*>(in), q, scales, M, static_cast<int>(K), KB);
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
+}
+
+int gi8_quantize_token(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K, void* stream)
+{
+    if (int rc = check_quant(in, in_dtype, q, scales, M, K)) return rc;
+    if (M == 0 || K == 0) return GI8_OK;
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int64_t blocks = M;
+    const int64_t cap = static_cast<int64_t>(st->sm_count) * 8;
+    if (blocks > cap) blocks = cap;
+    if (in_dtype == 0)
+        quantize_token_row_kernel<float><<<static_cast<int>(blocks), kQuantThreads, 0, s>>>(static_cast<const float*>(in), q,
+                                                                                         scales, M, static_cast<int>(K));
+    else
+        quantize_token_row_kernel<__nv_bfloat16><<<static_cast<int>(blocks), kQuantThreads, 0, s>>>(
+            static_cast<const __nv_bfloat16*>(in), q, scales, M, static_cast<int>(K));
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
 }
 
 int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,

@@ -323,6 +323,8 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         fence_proxy_async_smem();
         prefetch_tensormap(&map_w);
         prefetch_tensormap(&map_x);
+        pdl_launch_dependents();  // the next kernel may be scheduled as soon as SMs free up
+        pdl_wait();               // everything above overlapped the previous kernel's tail; global reads start here
         const uint64_t pol_w = l2_policy_evict_first();
         const uint64_t pol_x = l2_policy_evict_last();
         const int first = min(num_kb, STAGES);
@@ -340,6 +342,7 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     tcgen05_fence_before_sync();
     __syncthreads();
     tcgen05_fence_after_sync();
+    pdl_wait();  // every thread: scales are read and the output is written only after the previous kernel is done
     const uint32_t tmem_base = tmem_base_slot;
     int32_t* partial = reinterpret_cast<int32_t*>(smem);  // [MT][128], reuses the pipeline buffers once drained
 

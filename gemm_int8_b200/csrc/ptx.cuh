@@ -38,6 +38,13 @@ GI8_DEVICE bool elect_one()
     return pred != 0;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization attribute may
+// start while the previous kernel in the stream is still draining; every thread must pass pdl_wait() before it
+// touches global memory that an earlier kernel may have written (or overwrites memory an earlier kernel reads).
+// pdl_launch_dependents() tells the runtime that the NEXT kernel's CTAs may be scheduled as SMs free up.
+GI8_DEVICE void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+GI8_DEVICE void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ---------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------

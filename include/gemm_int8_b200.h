@@ -113,6 +113,17 @@ int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, 
                              int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * Activation quantisers that feed the W8A8 entry points (the reference ships none; its benchmark only rounds and
+ * clamps, benchmark.py:17-18).  Rule: s = amax / 127 (s = 1 where the block is all zero),
+ * q = clamp(round_half_even(v / s), -127, 127).  `in` is row-major [M,K], fp32 (in_dtype 0) or bf16 (in_dtype 1),
+ * 16-byte aligned rows (K % 8 == 0 for bf16, K % 4 == 0 for fp32); q int8 [M,K] 4-byte aligned.
+ *   gi8_quantize_token_block : one scale per row per 128-wide K block, scales fp32 [M, ceil(K/128)]
+ *   gi8_quantize_token       : one scale per row, scales fp32 [M]
+ */
+int gi8_quantize_token_block(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K, void* stream);
+int gi8_quantize_token(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K, void* stream);
+
+/*
  * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted
  * per-shape dispatch that replaces the reference's shape table (csrc/kernels/gemm.cu:136-161).
  * Names: "dense_bn256", "dense_bn128", "dense_bn64", "smallm" (split-K through global scratch),

@@ -409,3 +409,53 @@ def test_error_paths(g):
     with pytest.raises(RuntimeError):
         g.matmul_scaled(x, y, torch.rand(64).cuda().double(), torch.rand(72).cuda())
     assert g.device_status() == 0
+
+
+# ---------------------------------------------------------------------------------------- callers of the GEMM
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_quantiser_kernels_match_oracle(g, oracle, dtype):
+    gen = torch.Generator().manual_seed(101)
+    for (M, K) in [(1, 128), (7, 136), (33, 4096), (300, 1000 if dtype == torch.float32 else 1008), (64, 14336)]:
+        a = (torch.randn(M, K, generator=gen) * 3).to(dtype)
+        a[0, : min(K, 128)] = 0  # an all-zero block: scale 1, zeros
+        af = a.float()
+        q, s = g.quantize_per_token_block(a.cuda())
+        qr, sr = oracle.c_quantize_blocks(af, 1, 128)
+        assert np.array_equal(q.cpu().numpy(), qr) and np.array_equal(s.cpu().numpy(), sr), (dtype, M, K)
+        q, s = g.quantize_per_token(a.cuda())
+        qr, sr = oracle.c_quantize_blocks(af, 1, K)
+        assert np.array_equal(q.cpu().numpy(), qr) and np.array_equal(s.cpu().numpy(), sr.reshape(-1)), (dtype, M, K)
+    with pytest.raises(RuntimeError):
+        g.quantize_per_token_block(torch.zeros(4, 130).cuda())       # K % 4 != 0
+    with pytest.raises(RuntimeError):
+        g.quantize_per_token_block(torch.zeros(4, 128))              # CPU tensor
+
+
+def test_int8_linear_matches_oracle_pipeline(g, oracle):
+    """Int8Linear = offline weight quantiser + fused activation quantiser + GEMM; every stage has an oracle, so
+    the layer output must equal the oracle pipeline bit for bit, and stay close to the fp32 linear layer."""
+    from gemm_int8_b200 import quant
+
+    gen = torch.Generator().manual_seed(202)
+    x = torch.randn(3, 50, 1024, generator=gen)
+    w = torch.randn(520, 1024, generator=gen) * 0.02
+    layer = g.Int8Linear.from_float(w, mode="blockwise").cuda()
+    y = layer(x.cuda())
+    assert y.shape == (3, 50, 520) and y.dtype == torch.bfloat16
+    xq, xs = oracle.c_quantize_blocks(x.reshape(-1, 1024), 1, 128)
+    wq, ws = oracle.c_quantize_blocks(w, 128, 128)
+    ref = oracle.c_matmul_blockwise(xq, wq, xs, ws)
+    assert np.array_equal(oracle.bf16_bits(y.reshape(-1, 520)), ref)
+    dense = (x.reshape(-1, 1024) @ w.t())
+    rel = (y.reshape(-1, 520).float().cpu() - dense).norm() / dense.norm()
+    assert rel < 0.02, rel
+
+    layer_c = g.Int8Linear.from_float(w, bias=torch.ones(520), mode="channel", out_dtype=torch.float32).cuda()
+    y2 = layer_c(x[0, :4].cuda())
+    xq, xs = oracle.c_quantize_blocks(x[0, :4], 1, 1024)
+    wq, ws = quant.quantize_per_row(w)
+    ref2 = oracle.to_torch_bf16(oracle.c_matmul_scaled(xq, wq, xs.reshape(-1), ws)) + torch.ones(520).bfloat16()
+    assert y2.dtype == torch.float32 and torch.equal(y2.cpu(), ref2.float())
+
+    compiled = torch.compile(layer, dynamic=True)
+    assert torch.equal(compiled(x.cuda()), y)
