@@ -130,19 +130,23 @@ int check_common(const void* x, const void* y, const void* out, int64_t M, int64
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Dispatch: picks the tile width for the dense/blockwise kernels.  Model: the grid runs
-// ceil(tiles / SMs) waves; a wave of 128 x BN tiles costs about (BN + fixed overhead) per K block.
+// Dispatch: picks the tile width for the dense/blockwise kernels.  Model fitted on B200: the grid runs
+// ceil(tiles / SMs) waves; a wave of 128 x BN tiles costs BN x c(BN) + a fixed part per K block, where c is the
+// measured inefficiency of the narrower tensor-core instruction (its shared-memory operand traffic per MAC is
+// higher): dense 2900 / 1750 / 1000 TOP/s at BN = 256 / 128 / 64, blockwise 1450 / 1100 at BN = 256 / 128.
 // ---------------------------------------------------------------------------------------------------
-int pick_bn(int64_t M, int64_t N, int sms, bool allow64)
+int pick_bn(int64_t M, int64_t N, int sms, bool blockwise)
 {
     const int cand[3] = {256, 128, 64};
+    const double ineff_dense[3] = {1.0, 1.65, 2.9};
+    const double ineff_block[3] = {1.0, 1.35, 0.0};
     int best = 256;
     double best_cost = 1e300;
-    for (int i = 0; i < (allow64 ? 3 : 2); ++i) {
+    for (int i = 0; i < (blockwise ? 2 : 3); ++i) {
         const int bn = cand[i];
         const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
         const int64_t waves = (tiles + sms - 1) / sms;
-        const double cost = static_cast<double>(waves) * (bn + 24);
+        const double cost = static_cast<double>(waves) * (bn * (blockwise ? ineff_block[i] : ineff_dense[i]) + 16.0);
         if (cost < best_cost) best_cost = cost, best = bn;
     }
     return best;
@@ -200,7 +204,7 @@ int dispatch_dense(DeviceState* st, const int8_t* x, const int8_t* y, DenseParam
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
         case VAR_DENSE_BN64: bn = 64; break;
-        default: bn = pick_bn(p.M, p.N, st->sm_count, true);
+        default: bn = pick_bn(p.M, p.N, st->sm_count, false);
     }
     if (bn == 256) return launch_dense<256, 4, EPI>(st, EPI * 3 + 0, x, y, p, stream);
     if (bn == 128) return launch_dense<128, 6, EPI>(st, EPI * 3 + 1, x, y, p, stream);
@@ -247,7 +251,7 @@ SmallMPlan plan_smallm(int64_t M, int64_t N, int64_t K, int sms, bool forced, in
     const int slots = 2 * sms;
     int splits = slots / pl.tiles_n;
     if (splits < 1) splits = 1;
-    if (splits <= 2 && M >= 16) splits = 1;
+    if (splits <= 2) splits = 1;  // many weight tiles already fill the machine; a second split only adds a reduction
     if (splits > kb_total / 2) splits = kb_total / 2 > 0 ? kb_total / 2 : 1;
     if (splits > max_splits) splits = max_splits;
     if (const char* e = getenv("GEMM_INT8_SPLITS")) {  // tuning override
@@ -379,7 +383,7 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
     if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
     if (g_forced_variant != VAR_AUTO) return kVariantNames[g_forced_variant];
     if (kind == 1 && plan_smallm(M, N, K, sms, false).use) return "smallm_cluster";
-    const int bn = pick_bn(M, N, sms, kind != 2);
+    const int bn = pick_bn(M, N, sms, kind == 2);
     return bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
 }
 
@@ -636,7 +640,7 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     switch (g_forced_variant) {
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
-        default: bn = pick_bn(M, N, st->sm_count, false);
+        default: bn = pick_bn(M, N, st->sm_count, true);
     }
     p.tiles_m = (int)((M + kBM - 1) / kBM);
     p.tiles_n = (int)((N + bn - 1) / bn);
