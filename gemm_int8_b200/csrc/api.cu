@@ -133,13 +133,13 @@ int check_common(const void* x, const void* y, const void* out, int64_t M, int64
 // Dispatch: picks the tile width for the dense/blockwise kernels.  Model fitted on B200: the grid runs
 // ceil(tiles / SMs) waves; a wave of 128 x BN tiles costs BN x c(BN) + a fixed part per K block, where c is the
 // measured inefficiency of the narrower tensor-core instruction (its shared-memory operand traffic per MAC is
-// higher): dense 2900 / 1750 / 1000 TOP/s at BN = 256 / 128 / 64, blockwise 1450 / 1100 at BN = 256 / 128.
+// higher): dense 2900 / 1750 / 1000 TOP/s at BN = 256 / 128 / 64, blockwise 1550 / 1400 at BN = 256 / 128.
 // ---------------------------------------------------------------------------------------------------
 int pick_bn(int64_t M, int64_t N, int sms, bool blockwise)
 {
     const int cand[3] = {256, 128, 64};
     const double ineff_dense[3] = {1.0, 1.65, 2.9};
-    const double ineff_block[3] = {1.0, 1.35, 0.0};
+    const double ineff_block[3] = {1.0, 1.12, 0.0};
     int best = 256;
     double best_cost = 1e300;
     for (int i = 0; i < (blockwise ? 2 : 3); ++i) {
@@ -346,6 +346,16 @@ extern "C" {
 
 #ifdef GI8_ENABLE_ABLATIONS
 // Tuning builds only (not declared in the public header): copies out and clears the pair kernel's wait counters.
+int gi8_debug_bw_counters(unsigned long long* out, int n)
+{
+    if (n > 148 * 8) n = 148 * 8;
+    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
+    if (cudaMemcpyFromSymbol(out, gi8::g_bw_dbg, sizeof(unsigned long long) * n) != cudaSuccess) return 1;
+    static unsigned long long zeros[148 * 8] = {};
+    if (cudaMemcpyToSymbol(gi8::g_bw_dbg, zeros, sizeof(zeros)) != cudaSuccess) return 1;
+    return 0;
+}
+
 int gi8_debug_pair_counters(unsigned long long* out, int n)
 {
     if (n > 148 * 8) n = 148 * 8;

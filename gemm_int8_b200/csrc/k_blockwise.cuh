@@ -5,21 +5,22 @@
 // semantics are those of the CPU oracle's blockwise restatement.
 //
 // Structure (one persistent CTA per SM, 640 threads = 5 warpgroups):
-//   warpgroup 0 control: warp 0 TMA producer (as in the dense kernel); warp 1 MMA issuer -- per K block, four
-//               tcgen05.mma kind::i8 that overwrite one of NBUF = 512 / BN tensor-memory partial buffers, then a
-//               commit to that buffer's barrier; warp 2 allocates tensor memory; the group gives most of its
-//               registers back (setmaxnreg.dec).
+//   warpgroup 0 control: warp 0 TMA producer (as in the dense kernel); warps 1 and 3 MMA issuers taking alternate
+//               K blocks -- per K block, four tcgen05.mma kind::i8 that overwrite one of NBUF = 512 / BN
+//               tensor-memory partial buffers, then ONE commit that both frees the pipeline stage and publishes
+//               the partial; warp 2 allocates tensor memory; the group gives most of its registers back
+//               (setmaxnreg.dec).
 //   warps 4..19 promotion (16 warps, setmaxnreg.inc): tcgen05.ld the int32 partial, hand the buffer back to the
 //               MMA warp as soon as the loads have landed in registers, then convert to fp32 and fma with the
 //               block's scale into fp32 register accumulators.  Warp w owns TMEM lane quarter (w % 4) and column
 //               quarter ((w - 4) / 4) of the tile; a column quarter never straddles a 128-wide weight-scale
 //               block.  At the end of the tile the same warps cast to bf16 and store.
 //
-// What bounds it (measured): the hand-over chain commit -> promotion warps wake -> load -> arrive -> MMA thread
-// wakes -> next MMA starts costs about 1000 cycles per K block whatever the arithmetic, against ~750 cycles of
-// tensor-core time per 128 x 256 x 128 block; with B partial buffers the period per K block is
-// max(MMA, (MMA + hand-over + load) / B, promotion issue time), so the buffers are released before the arithmetic
-// and the narrower tile (four buffers) is preferred where its MMA efficiency allows.
+// What bounds it (measured with cycle counters in a tuning build, 128 x 256 tile): the tensor core needs ~750 cycles
+// per K block; ONE issuing thread needed ~240-580 cycles for the four MMAs plus ~170 per commit, in series with its
+// two waits (hence two issuers and a single commit); the promotion warps need ~1230 cycles per K block -- 512
+// tensor-memory loads and 2 x 256 arithmetic warp-instructions per scheduler at ~0.65 instructions per cycle
+// (cvt.rn.f32.s32 issues at half rate) -- and are the bound that remains.
 #pragma once
 
 #include "k_dense.cuh"
@@ -103,6 +104,15 @@ GI8_DEVICE void setmaxnreg_dec()
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+#ifdef GI8_ENABLE_ABLATIONS
+// Tuning builds: per-CTA cycle counters (MMA thread: 0 wait-empty-buffer, 1 wait-stage, 2 issue, 3 commits, 4 count;
+// promotion warp 4: 5 wait-partial, 6 rest of the K block, 7 count).
+__device__ unsigned long long g_bw_dbg[148 * 8];
+#define GI8_BW_DBG(slot, v) atomicAdd(&g_bw_dbg[blockIdx.x * 8 + (slot)], (unsigned long long)(v))
+#else
+#define GI8_BW_DBG(slot, v) ((void)0)
+#endif
+
 template <int BN, int STAGES, int PROMO>
 __global__ void __launch_bounds__(kBlockwiseThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
@@ -122,8 +132,10 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
     __shared__ __align__(8) uint64_t bar_full[STAGES];
-    __shared__ __align__(8) uint64_t bar_empty[STAGES];
-    __shared__ __align__(8) uint64_t bar_part_full[NBUF];
+    // bar_done[s]: the MMAs of the K block that used stage s have completed -- the stage may be reloaded (the
+    // producer waits on it) AND the K block's partial is complete in tensor memory (the promotion warps wait on it).
+    // One tcgen05.commit per K block serves both.
+    __shared__ __align__(8) uint64_t bar_done[STAGES];
     __shared__ __align__(8) uint64_t bar_part_empty[NBUF];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
@@ -137,10 +149,9 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_empty[s], 1);
+            mbar_init(&bar_done[s], 1);
         }
         for (int b = 0; b < NBUF; ++b) {
-            mbar_init(&bar_part_full[b], 1);
             mbar_init(&bar_part_empty[b], kPromoWarps);
         }
         fence_barrier_init();
@@ -169,7 +180,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     for (int kb = 0; kb < num_kb; ++kb, ++it) {
                         const uint32_t s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
-                        if (!wait_or_abort(&bar_empty[s], ph ^ 1, &abort_flag)) {
+                        if (!wait_or_abort(&bar_done[s], ph ^ 1, &abort_flag)) {
                             raise_error(p.status, &abort_flag, ERR_TIMEOUT_PRODUCER);
                             ok = false;
                             break;
@@ -189,34 +200,47 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     }
                 }
             }
-        } else if (warp == 1) {
-            // -------------------------------------------------------------- MMA issuer
+        } else if (warp == 1 || warp == 3) {
+            // -------------------------------------------------------------- MMA issuers
+            // Issuing the four MMAs of a K block and committing them costs one thread several hundred cycles
+            // (more when its scheduler is busy with promotion warps), which is of the order of the tensor-core
+            // time of the block itself.  Two threads on different schedulers therefore take alternate K blocks:
+            // each owns the tensor-memory buffers and pipeline stages of its parity, so no ordering between the
+            // two is needed.
+            static_assert(STAGES % 2 == 0 && NBUF % 2 == 0, "K blocks of one parity must map to stages/buffers of that parity");
             if (lane == 0) {
-                uint32_t it = 0;  // running K-block counter: selects both the smem stage and the TMEM buffer
-                bool ok = true;
-                for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                        const uint32_t s = it % STAGES;
-                        const uint32_t ph = (it / STAGES) & 1;
-                        const uint32_t buf = it % NBUF;
-                        const uint32_t bph = (it / NBUF) & 1;
-                        if (!wait_or_abort(&bar_part_empty[buf], bph ^ 1, &abort_flag) ||
-                            !wait_or_abort(&bar_full[s], ph, &abort_flag)) {
-                            raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
-                            ok = false;
-                            break;
-                        }
-                        tcgen05_fence_after_sync();
-                        const uint32_t tmem_d = tmem_base + buf * BN;
-                        const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
-                        const uint64_t da = make_smem_desc_k128(a_addr);
-                        const uint64_t db = make_smem_desc_k128(a_addr + kBytesA);
-#pragma unroll
-                        for (int k = 0; k < kBK / kUmmaK; ++k)
-                            umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, k != 0 ? 1u : 0u);
-                        umma_commit(&bar_empty[s]);
-                        umma_commit(&bar_part_full[buf]);
+                const uint32_t parity = warp == 1 ? 0u : 1u;
+                int my_tiles = 0;
+                for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) ++my_tiles;
+                const uint32_t total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(num_kb);
+                for (uint32_t it = parity; it < total; it += 2) {
+                    const uint32_t s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    const uint32_t buf = it % NBUF;
+                    const uint32_t bph = (it / NBUF) & 1;
+                    const long long c0 = clock64();
+                    const bool w1 = wait_or_abort(&bar_part_empty[buf], bph ^ 1, &abort_flag);
+                    const long long c1 = clock64();
+                    if (!w1 || !wait_or_abort(&bar_full[s], ph, &abort_flag)) {
+                        raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
+                        break;
                     }
+                    const long long c2 = clock64();
+                    tcgen05_fence_after_sync();
+                    const uint32_t tmem_d = tmem_base + buf * BN;
+                    const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
+                    const uint64_t da = make_smem_desc_k128(a_addr);
+                    const uint64_t db = make_smem_desc_k128(a_addr + kBytesA);
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k)
+                        umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, k != 0 ? 1u : 0u);
+                    const long long c3 = clock64();
+                    umma_commit(&bar_done[s]);
+                    GI8_BW_DBG(0, c1 - c0);
+                    GI8_BW_DBG(1, c2 - c1);
+                    GI8_BW_DBG(2, c3 - c2);
+                    GI8_BW_DBG(3, clock64() - c3);
+                    GI8_BW_DBG(4, 1);
                 }
             }
         }
@@ -237,9 +261,10 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         // is already in flight, so neither the tensor-memory load latency nor the hand-over to the MMA warp sits
         // in front of the arithmetic.  A buffer is handed back as soon as its last chunk is in registers.
         uint32_t va[kChunk], vb[kChunk];
+        long long dbg_t = clock64();
         const int first_tile = blockIdx.x;
         if (first_tile < num_tiles) {
-            if (!wait_or_abort(&bar_part_full[0], 0, &abort_flag)) {
+            if (!wait_or_abort(&bar_done[0], 0, &abort_flag)) {
                 if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
                 ok = false;
             }
@@ -330,11 +355,15 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                         const bool have_next = (kb + 1 < num_kb) || !last_tile;
                         if (have_next) {
                             const uint32_t nit = it + 1;
-                            if (!wait_or_abort(&bar_part_full[nit % NBUF], (nit / NBUF) & 1, &abort_flag)) {
+                            const long long w0 = clock64();
+                            if (warp == 4 && lane == 0) { GI8_BW_DBG(6, w0 - dbg_t); }
+                            if (!wait_or_abort(&bar_done[nit % STAGES], (nit / STAGES) & 1, &abort_flag)) {
                                 if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
                                 ok = false;
                             }
                             ok = __all_sync(0xffffffffu, ok);
+                            dbg_t = clock64();
+                            if (warp == 4 && lane == 0) { GI8_BW_DBG(5, dbg_t - w0); GI8_BW_DBG(7, 1); }
                             if (ok) {
                                 tcgen05_fence_after_sync();
                                 tmem_ld_32x32b_x16(tmem_base + lane_base + (nit % NBUF) * BN + cg * CW, va);
