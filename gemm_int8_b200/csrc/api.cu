@@ -177,21 +177,45 @@ int ensure_smem(DeviceState* st, int slot, Kernel kernel, size_t bytes)
     return GI8_OK;
 }
 
+// Tensor map over the bf16 output [M, N] (row stride ldo elements) for the epilogue's TMA stores: 32 x 32 boxes,
+// 64-byte swizzle.
+int make_output_map(CUtensorMap* map, void* out, int64_t M, int64_t N, int64_t ldo)
+{
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldo) * 2};
+    cuuint32_t box[2] = {32, 32};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(GI8_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
+    return GI8_OK;
+}
+
 template <int BN, int STAGES, int EPI>
 int launch_dense(DeviceState* st, int slot, const int8_t* x, const int8_t* y, DenseParams p, cudaStream_t stream)
 {
-    constexpr size_t smem = static_cast<size_t>(STAGES) * (kBM + BN) * kBK + 1024;
+    constexpr size_t kStoreStage = 4 * 2 * 2048;  // four epilogue warps x two 32 x 64-byte blocks
+    constexpr size_t smem = static_cast<size_t>(STAGES) * (kBM + BN) * kBK + kStoreStage + 1024;
     auto kernel = dense_gemm_kernel<BN, STAGES, EPI>;
     if (int rc = ensure_smem(st, slot, kernel, smem)) return rc;
-    CUtensorMap mx, my;
+    CUtensorMap mx, my, mo;
     if (int rc = make_operand_map(&mx, x, p.M, p.K, kBM)) return rc;
     if (int rc = make_operand_map(&my, y, p.N, p.K, BN)) return rc;
+    // bf16 epilogues store through TMA when the output rows are 16-byte aligned (GEMM_INT8_TMA_STORE=0: plain stores)
+    const char* ts = getenv("GEMM_INT8_TMA_STORE");
+    p.tma_store = (EPI != EPI_RAW_I32) && p.vec_ok && !(ts && ts[0] == '0');
+    if (p.tma_store) {
+        if (int rc = make_output_map(&mo, p.out, p.M, p.N, p.ldo)) return rc;
+    } else {
+        mo = mx;  // unused by the kernel
+    }
     p.tiles_m = (p.M + kBM - 1) / kBM;
     p.tiles_n = (p.N + BN - 1) / BN;
     p.group_m = pick_group_m(p.K);
     const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
-    kernel<<<grid, kDenseThreads, smem, stream>>>(mx, my, p);
+    kernel<<<grid, kDenseThreads, smem, stream>>>(mx, my, mo, p);
     GI8_CUDA(cudaGetLastError());
     return GI8_OK;
 }

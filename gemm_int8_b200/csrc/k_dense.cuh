@@ -48,6 +48,7 @@ struct DenseParams {
     int tiles_m, tiles_n;
     int vec_ok;           // out is 16-byte aligned and ldo keeps every row 16-byte aligned
     int group_m;          // row-blocks per rasterisation band
+    int tma_store;        // bf16 epilogues: stage 32 x 32 blocks in shared memory and write them with TMA stores
     float alpha;
 };
 
@@ -89,7 +90,7 @@ GI8_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb
 template <int BN, int STAGES, int EPI>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                  const DenseParams p)
+                  const __grid_constant__ CUtensorMap map_out, const DenseParams p)
 {
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
     constexpr uint32_t kBytesA = kBM * kBK;
@@ -102,6 +103,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     extern __shared__ uint8_t smem_raw[];
     // 128B-swizzled tiles need 1024-byte alignment.
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Behind the pipeline stages: per epilogue warp two 32-row x 64-byte staging blocks for TMA stores.
+    uint8_t* store_stage = smem + STAGES * kStageBytes;
 
     __shared__ __align__(8) uint64_t bar_full[STAGES];
     __shared__ __align__(8) uint64_t bar_empty[STAGES];
@@ -128,6 +131,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         fence_barrier_init();
         prefetch_tensormap(&map_x);
         prefetch_tensormap(&map_y);
+        if (p.tma_store) prefetch_tensormap(&map_out);
     }
     if (warp == 1) {
         tmem_alloc(&tmem_base_slot, kTmemCols);
@@ -237,8 +241,9 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 tmem_ld_32x32b_x32(taddr + c, v);
                 tmem_ld_wait();
                 const int col0 = nb * BN + c;
-                if (!row_ok || col0 >= p.N) continue;
+                if (col0 >= p.N) continue;  // warp-uniform
                 if constexpr (EPI == EPI_RAW_I32) {
+                    if (!row_ok) continue;
                     int32_t* dst = static_cast<int32_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
                     if (col0 + 32 <= p.N && p.vec_ok) {
 #pragma unroll
@@ -261,6 +266,32 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                             f[j] = a * (row_scale * cs);
                         }
                     }
+                    if (p.tma_store) {
+                        // 32 rows x 32 bf16 of this warp go to shared memory in the 64-byte-swizzled layout the
+                        // output tensor map expects (16-byte chunk index xor (row / 2) % 4: conflict-free), then one
+                        // lane issues the TMA store; rows and columns beyond M and N are clipped by the hardware.
+                        const int row0 = mb * kBM + quarter * 32;
+                        if (row0 < p.M) {
+                            uint8_t* stg = store_stage + ((warp - 2) * 2 + ((c >> 5) & 1)) * 2048;
+                            if (lane == 0) tma_store_wait_read<1>();  // the block staged two chunks ago has been read
+                            __syncwarp();
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const int cq = q ^ ((lane >> 1) & 3);
+                                *reinterpret_cast<uint4*>(stg + lane * 64 + cq * 16) = make_uint4(
+                                    pack_bf16x2(f[8 * q], f[8 * q + 1]), pack_bf16x2(f[8 * q + 2], f[8 * q + 3]),
+                                    pack_bf16x2(f[8 * q + 4], f[8 * q + 5]), pack_bf16x2(f[8 * q + 6], f[8 * q + 7]));
+                            }
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                tma_store_2d(&map_out, stg, col0, row0);
+                                tma_store_commit();
+                            }
+                        }
+                        continue;
+                    }
+                    if (!row_ok) continue;
                     uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col0;
                     if (col0 + 32 <= p.N && p.vec_ok) {
 #pragma unroll
@@ -280,6 +311,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_acc_empty[buf]);
         }
+        // Outstanding TMA stores read this CTA's shared memory: they must have completed before it exits.
+        if (lane == 0) tma_store_wait_all<0>();
     }
 
     tcgen05_fence_before_sync();
