@@ -681,6 +681,16 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     p.group_m = pick_group_m(p.K);
     const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+    CUtensorMap mo;
+    {
+        const char* ts = getenv("GEMM_INT8_TMA_STORE");
+        p.tma_store = p.vec_ok && !(ts && ts[0] == '0');
+        if (p.tma_store) {
+            if (int rc = make_output_map(&mo, out, M, N, N)) return rc;
+        } else {
+            mo = mx;  // unused by the kernel
+        }
+    }
     // Tuning knob (not part of the ABI): GEMM_INT8_PROMOTION = 0 | 1 | 2 selects the promotion arithmetic
     // (3 and 4 are measurement-only ablations that produce wrong results).
     int promo = PROMO_I2F;
@@ -688,10 +698,10 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     if (make_operand_map(&my, y, N, K, bn)) return GI8_ERR_CUDA;
 #define GI8_LAUNCH_BW(BN_, ST_, PR_, SLOT_)                                                   \
     do {                                                                                     \
-        constexpr size_t smem = ST_ * (kBM + BN_) * kBK + 1024;                              \
+        constexpr size_t smem = ST_ * (kBM + BN_) * kBK + kPromoWarps * 2048 + 1024;         \
         auto kernel = blockwise_gemm_kernel<BN_, ST_, PR_>;                                  \
         if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                        \
-        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, p);                             \
+        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, mo, p);                         \
     } while (0)
     if (promo < PROMO_MAGIC || promo > PROMO_ABLATE_CVT_ONLY) promo = PROMO_I2F;
 #ifndef GI8_ENABLE_ABLATIONS

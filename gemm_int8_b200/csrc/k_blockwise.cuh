@@ -64,6 +64,7 @@ struct BlockwiseParams {
     int tiles_m, tiles_n;
     int vec_ok;  // out is 16-byte aligned and ldo % 8 == 0
     int group_m; // row-blocks per rasterisation band
+    int tma_store;  // stage 32 x 32 bf16 blocks in shared memory and write them with TMA stores
 };
 
 GI8_DEVICE uint64_t pack_f32x2(uint32_t lo_bits, uint32_t hi_bits)
@@ -116,7 +117,7 @@ __device__ unsigned long long g_bw_dbg[148 * 8];
 template <int BN, int STAGES, int PROMO>
 __global__ void __launch_bounds__(kBlockwiseThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                      const BlockwiseParams p)
+                      const __grid_constant__ CUtensorMap map_out, const BlockwiseParams p)
 {
     static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
     constexpr int NBUF = 512 / BN;  // partial buffers in tensor memory (2 or 4)
@@ -130,6 +131,8 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // Behind the pipeline stages: one 32-row x 64-byte staging block per promotion warp for TMA stores (its
+    // address is recomputed where it is used, to keep it out of the promotion loop's registers).
 
     __shared__ __align__(8) uint64_t bar_full[STAGES];
     // bar_done[s]: the MMAs of the K block that used stage s have completed -- the stage may be reloaded (the
@@ -263,18 +266,6 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         uint32_t va[kChunk], vb[kChunk];
         long long dbg_t = clock64();
         const int first_tile = blockIdx.x;
-        if (first_tile < num_tiles) {
-            if (!wait_or_abort(&bar_done[0], 0, &abort_flag)) {
-                if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
-                ok = false;
-            }
-            ok = __all_sync(0xffffffffu, ok);
-            if (ok) {
-                tcgen05_fence_after_sync();
-                tmem_ld_32x32b_x16(tmem_base + lane_base + cg * CW, va);
-                tmem_ld_wait();
-            }
-        }
 
         for (int tile = first_tile; tile < num_tiles && ok; tile += gridDim.x) {
             int mb, nb;
@@ -286,7 +277,17 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             const bool cols_ok = col_base < p.N;
             const float* sa_row = p.sa + static_cast<int64_t>(row_ok ? row : 0) * p.ld_sa;
             const float* sw_row = p.sw + static_cast<int64_t>(cols_ok ? col_base / 128 : 0) * p.ld_sw;
-            const bool last_tile = tile + static_cast<int>(gridDim.x) >= num_tiles;
+
+            // First chunk of the tile's first K block (not issued from the previous tile's last chunk: the
+            // epilogue then runs without a chunk in flight, which it has no registers for).
+            if (!wait_or_abort(&bar_done[it % STAGES], (it / STAGES) & 1, &abort_flag)) {
+                if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
+                ok = false;
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tcgen05_fence_after_sync();
+            tmem_ld_32x32b_x16(tmem_base + lane_base + (it % NBUF) * BN + cg * CW, va);
 
             float acc[CW];
 #pragma unroll
@@ -294,6 +295,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
             float sa_next = __ldg(sa_row);
             float sw_next = __ldg(sw_row);
+            tmem_ld_wait();
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
                 float t = sa_next * sw_next;  // fp32, round to nearest: the scale of this K block
                 if constexpr (PROMO == PROMO_ABLATE_SCALES) t = 0.5f;
@@ -352,7 +354,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                         tcgen05_fence_before_sync();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(&bar_part_empty[it % NBUF]);
-                        const bool have_next = (kb + 1 < num_kb) || !last_tile;
+                        const bool have_next = kb + 1 < num_kb;
                         if (have_next) {
                             const uint32_t nit = it + 1;
                             const long long w0 = clock64();
@@ -379,7 +381,45 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             }
             if (!ok) break;
 
-            if (row_ok && cols_ok) {
+            if (p.tma_store) {
+                // 32 x 32 blocks through 64-byte-swizzled shared memory and TMA stores (rows >= M and columns >= N
+                // are clipped by the hardware); see the dense kernel's epilogue for the layout.  The tile's
+                // coordinates are derived again from an opaque copy of the tile index so that they do not occupy
+                // registers across the promotion loop.
+                int tile_again = tile, mb2, nb2;
+                asm volatile("" : "+r"(tile_again));
+                tile_coords(tile_again, p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
+                const int row0 = mb2 * kBM + quarter * 32;
+                const int col_base = nb2 * BN + cg * CW;
+                if (row0 < p.M && col_base < p.N) {
+                    const uint32_t stg = ((smem_u32(smem_raw) + 1023u) & ~1023u) + STAGES * kStageBytes + (warp - 4) * 2048;
+#pragma unroll
+                    for (int c = 0; c < CW; c += 32) {
+                        if (col_base + c >= p.N) break;
+                        if (lane == 0) tma_store_wait_read<0>();
+                        __syncwarp();
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            const int cq = q ^ ((lane >> 1) & 3);
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * 64 + cq * 16),
+                                         "r"(pack_bf16x2(acc[c + 8 * q], acc[c + 8 * q + 1])),
+                                         "r"(pack_bf16x2(acc[c + 8 * q + 2], acc[c + 8 * q + 3])),
+                                         "r"(pack_bf16x2(acc[c + 8 * q + 4], acc[c + 8 * q + 5])),
+                                         "r"(pack_bf16x2(acc[c + 8 * q + 6], acc[c + 8 * q + 7]))
+                                         : "memory");
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                             reinterpret_cast<uint64_t>(&map_out)),
+                                         "r"(stg), "r"(col_base + c), "r"(row0)
+                                         : "memory");
+                            tma_store_commit();
+                        }
+                    }
+                }
+            } else if (row_ok && cols_ok) {
                 uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col_base;
                 if (col_base + CW <= p.N && p.vec_ok) {
 #pragma unroll
@@ -395,6 +435,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             }
             __syncwarp();
         }
+        if (lane == 0) tma_store_wait_all<0>();  // stores read this CTA's shared memory: finish before exit
     }
 
     tcgen05_fence_before_sync();
