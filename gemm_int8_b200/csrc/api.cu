@@ -53,7 +53,7 @@ struct DeviceState {
     bool ready = false;
     int sm_count = 0;
     uint32_t* status = nullptr;
-    bool attr_set[32] = {};
+    bool attr_set[48] = {};
 };
 
 std::mutex g_mutex;
@@ -638,6 +638,9 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
                     (long long)ld_sa, (long long)ld_sw, (long long)KB);
     if (reinterpret_cast<uintptr_t>(sa) % 4 || reinterpret_cast<uintptr_t>(sw) % 4)
         return fail(GI8_ERR_MISALIGNED, "scale pointers must be 4-byte aligned");
+    // The kernels index the scale arrays with 32-bit element offsets.
+    if (M * ld_sa >= (int64_t(1) << 31) || ((N + 127) / 128) * ld_sw >= (int64_t(1) << 31))
+        return fail(GI8_ERR_INVALID_ARGUMENT, "scale arrays of 2^31 or more elements are not supported");
     BlockwiseParams p{};
     p.out = out, p.sa = sa, p.sw = sw, p.status = st->status, p.ldo = N, p.ld_sa = ld_sa, p.ld_sw = ld_sw;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
@@ -691,21 +694,29 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
             mo = mx;  // unused by the kernel
         }
     }
-    // Tuning knob (not part of the ABI): GEMM_INT8_PROMOTION = 0 | 1 | 2 selects the promotion arithmetic
-    // (3 and 4 are measurement-only ablations that produce wrong results).
-    int promo = PROMO_I2F;
+    // Tuning knobs (not part of the ABI; every combination gives bit-identical results):
+    //   GEMM_INT8_PROMOTION = 0 | 1 | 2 | 9   promotion arithmetic (default 9, the biased accumulator; 3..8 are
+    //                                         measurement-only ablations with wrong results, tuning builds only)
+    //   GEMM_INT8_PIPE      = 0 | 2           with promotion 2: double-buffered 16-column or single 32-column loads
+    //   GEMM_INT8_HALVES    = 1 | 2           256-wide tile: MMAs with N = 256, or two column halves with N = 128
+    int promo = PROMO_BIAS_X2;
     if (const char* e = getenv("GEMM_INT8_PROMOTION")) promo = atoi(e);
+    int pipe = bn == 256 ? PIPE_X32_SINGLE : PIPE_X16_DOUBLE;
+    if (const char* e = getenv("GEMM_INT8_PIPE")) pipe = atoi(e);
+    int split = 2;
+    if (const char* e = getenv("GEMM_INT8_HALVES")) split = atoi(e) == 1 ? 1 : 2;
     if (make_operand_map(&my, y, N, K, bn)) return GI8_ERR_CUDA;
-#define GI8_LAUNCH_BW(BN_, ST_, PR_, SLOT_)                                                   \
+#define GI8_LAUNCH_BW(BN_, ST_, PR_, SLOT_) GI8_LAUNCH_BWP(BN_, ST_, PR_, PIPE_X16_DOUBLE, 1, SLOT_)
+#define GI8_LAUNCH_BWP(BN_, ST_, PR_, PIPE_, SPLIT_, SLOT_)                                  \
     do {                                                                                     \
         constexpr size_t smem = ST_ * (kBM + BN_) * kBK + kPromoWarps * 2048 + 1024;         \
-        auto kernel = blockwise_gemm_kernel<BN_, ST_, PR_>;                                  \
+        auto kernel = blockwise_gemm_kernel<BN_, ST_, PR_, PIPE_, SPLIT_>;                   \
         if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                        \
         kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, mo, p);                         \
     } while (0)
-    if (promo < PROMO_MAGIC || promo > PROMO_ABLATE_CVT_ONLY) promo = PROMO_I2F;
+    if (promo < PROMO_MAGIC || promo > PROMO_BIAS_X2) promo = PROMO_BIAS_X2;
 #ifndef GI8_ENABLE_ABLATIONS
-    if (promo > PROMO_I2F) promo = PROMO_I2F;  // the ablation kernels (wrong results) exist only in tuning builds
+    if (promo > PROMO_I2F && promo != PROMO_BIAS_X2) promo = PROMO_BIAS_X2;  // ablation kernels: tuning builds only
 #endif
     if (bn == 256) {
         if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC, 13);
@@ -718,7 +729,11 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
         else if (promo == PROMO_ABLATE_FMA_ONLY) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_FMA_ONLY, 9);
         else if (promo == PROMO_ABLATE_CVT_ONLY) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_CVT_ONLY, 10);
 #endif
-        else GI8_LAUNCH_BW(256, 4, PROMO_I2F, 17);
+        else if (promo == PROMO_I2F && pipe == PIPE_X32_SINGLE && split == 2) GI8_LAUNCH_BWP(256, 4, PROMO_I2F, PIPE_X32_SINGLE, 2, 35);
+        else if (promo == PROMO_I2F && pipe == PIPE_X32_SINGLE) GI8_LAUNCH_BWP(256, 4, PROMO_I2F, PIPE_X32_SINGLE, 1, 32);
+        else if (promo == PROMO_I2F) GI8_LAUNCH_BW(256, 4, PROMO_I2F, 17);
+        else if (split == 2) GI8_LAUNCH_BWP(256, 4, PROMO_BIAS_X2, PIPE_X16_SINGLE, 2, 38);
+        else GI8_LAUNCH_BWP(256, 4, PROMO_BIAS_X2, PIPE_X16_SINGLE, 1, 39);
     } else {
         if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC, 18);
         else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC_X2, 19);
@@ -726,9 +741,12 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
         else if (promo == PROMO_ABLATE_HANDSHAKE) GI8_LAUNCH_BW(128, 6, PROMO_ABLATE_HANDSHAKE, 20);
         else if (promo == PROMO_ABLATE_LOAD) GI8_LAUNCH_BW(128, 6, PROMO_ABLATE_LOAD, 21);
 #endif
-        else GI8_LAUNCH_BW(128, 6, PROMO_I2F, 22);
+        else if (promo == PROMO_I2F && pipe == PIPE_X32_SINGLE) GI8_LAUNCH_BWP(128, 6, PROMO_I2F, PIPE_X32_SINGLE, 1, 33);
+        else if (promo == PROMO_I2F) GI8_LAUNCH_BW(128, 6, PROMO_I2F, 22);
+        else GI8_LAUNCH_BWP(128, 6, PROMO_BIAS_X2, PIPE_X32_SINGLE, 1, 40);
     }
 #undef GI8_LAUNCH_BW
+#undef GI8_LAUNCH_BWP
     GI8_CUDA(cudaGetLastError());
     return GI8_OK;
 }

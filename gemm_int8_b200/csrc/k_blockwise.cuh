@@ -49,6 +49,11 @@ enum Promotion : int {
     PROMO_ABLATE_MATH = 6,       // measurement only (wrong results): scale loads and tensor-memory loads, no arithmetic
     PROMO_ABLATE_FMA_ONLY = 7,   // measurement only (wrong results): one fma per element on the raw bits, no conversion
     PROMO_ABLATE_CVT_ONLY = 8,   // measurement only (wrong results): one cvt per element, folded with xor
+    // The partial buffers hold 0x4B400000 before the MMAs, which all accumulate: the tensor core delivers the bit
+    // pattern of fp32 (12582912 + P) and no integer instruction is left -- add.f32x2 of -12582912 and fma.f32x2,
+    // one issue slot per element instead of two.  The promotion warps write the constant back (tcgen05.st) behind
+    // every load.
+    PROMO_BIAS_X2 = 9,
 };
 
 constexpr uint32_t kMagicBits = 0x4B400000u;  // fp32 12582912.0 = 1.5 * 2^23: adding an integer |P| < 2^22 to the
@@ -93,6 +98,25 @@ GI8_DEVICE uint64_t fma_f32x2(uint64_t a, uint64_t b, uint64_t c)
     return r;
 }
 
+// acc{0,1} += (fp32 bits v{0,1} - 12582912) * t as one add.f32x2 and one fma.f32x2, kept together so that no more
+// than one intermediate pair is live at a time.
+GI8_DEVICE void promote_biased_pair(uint32_t v0, uint32_t v1, float t, float& acc0, float& acc1)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .b64 pv, pn, pt, pa;\n\t"
+        "mov.b64 pv, {%2, %3};\n\t"
+        "mov.b64 pn, {%5, %5};\n\t"
+        "mov.b64 pt, {%4, %4};\n\t"
+        "mov.b64 pa, {%0, %1};\n\t"
+        "add.rn.f32x2 pv, pv, pn;\n\t"
+        "fma.rn.f32x2 pa, pv, pt, pa;\n\t"
+        "mov.b64 {%0, %1}, pa;\n\t"
+        "}\n"
+        : "+f"(acc0), "+f"(acc1)
+        : "r"(v0), "r"(v1), "f"(t), "f"(-kMagicF32));
+}
+
 template <int N>
 GI8_DEVICE void setmaxnreg_inc()
 {
@@ -110,24 +134,41 @@ GI8_DEVICE void setmaxnreg_dec()
 // promotion warp 4: 5 wait-partial, 6 rest of the K block, 7 count).
 __device__ unsigned long long g_bw_dbg[148 * 8];
 #define GI8_BW_DBG(slot, v) atomicAdd(&g_bw_dbg[blockIdx.x * 8 + (slot)], (unsigned long long)(v))
+#define GI8_BW_CLOCK() clock64()
 #else
 #define GI8_BW_DBG(slot, v) ((void)0)
+#define GI8_BW_CLOCK() 0ll
 #endif
 
-template <int BN, int STAGES, int PROMO>
+// Makes a 32-bit value opaque to the optimiser at this point, so that later uses read the register instead of
+// recomputing the value.
+#define GI8_PIN(v) asm volatile("" : "+r"(v))
+
+enum PartialPipe : int { PIPE_X16_DOUBLE = 0, PIPE_X32_DOUBLE = 1, PIPE_X32_SINGLE = 2, PIPE_X16_SINGLE = 3 };
+
+// SPLIT = 2 (BN = 256 only): the MMAs of a K block are issued as two column halves (N = 128 each), each half with
+// its own commit and its own hand-back barrier.  The eight promotion warps of the first half then start half an
+// MMA time earlier and run out of phase with those of the second half, and the time from "partial buffer handed
+// back" to "next partial published" -- which, with two buffers, bounds the K-block period together with the
+// promotion time -- shrinks by the MMA time of the other half.
+template <int BN, int STAGES, int PROMO, int PIPE = PIPE_X16_DOUBLE, int SPLIT = 1>
 __global__ void __launch_bounds__(kBlockwiseThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                       const __grid_constant__ CUtensorMap map_out, const BlockwiseParams p)
 {
     static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
+    static_assert(SPLIT == 1 || (SPLIT == 2 && BN == 256), "column halves only for the 256-wide tile");
     constexpr int NBUF = 512 / BN;  // partial buffers in tensor memory (2 or 4)
+    constexpr int NSUB = BN / SPLIT;  // N of one MMA
     constexpr int CW = BN / 4;      // columns per promotion warp (64 or 32)
     constexpr bool kPacked = PROMO == PROMO_MAGIC_X2;
+    constexpr bool kBias = PROMO == PROMO_BIAS_X2;
+    static_assert(!kBias || PIPE == PIPE_X16_SINGLE || PIPE == PIPE_X32_SINGLE, "the constant is written back behind single-buffered loads");
     constexpr uint32_t kBytesA = kBM * kBK;
     constexpr uint32_t kBytesB = BN * kBK;
     constexpr uint32_t kStageBytes = kBytesA + kBytesB;
     constexpr uint32_t kTmemCols = 512;
-    constexpr uint32_t kIdesc = make_idesc_i8(kBM, BN, false);
+    constexpr uint32_t kIdesc = make_idesc_i8(kBM, NSUB, false);
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -138,8 +179,8 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     // bar_done[s]: the MMAs of the K block that used stage s have completed -- the stage may be reloaded (the
     // producer waits on it) AND the K block's partial is complete in tensor memory (the promotion warps wait on it).
     // One tcgen05.commit per K block serves both.
-    __shared__ __align__(8) uint64_t bar_done[STAGES];
-    __shared__ __align__(8) uint64_t bar_part_empty[NBUF];
+    __shared__ __align__(8) uint64_t bar_done[SPLIT][STAGES];
+    __shared__ __align__(8) uint64_t bar_part_empty[SPLIT][NBUF];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
 
@@ -152,10 +193,10 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&bar_full[s], 1);
-            mbar_init(&bar_done[s], 1);
+            for (int h = 0; h < SPLIT; ++h) mbar_init(&bar_done[h][s], 1);
         }
         for (int b = 0; b < NBUF; ++b) {
-            mbar_init(&bar_part_empty[b], kPromoWarps);
+            for (int h = 0; h < SPLIT; ++h) mbar_init(&bar_part_empty[h][b], kPromoWarps / SPLIT);
         }
         fence_barrier_init();
         prefetch_tensormap(&map_x);
@@ -169,6 +210,28 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
+    // Promotion warps in the biased mode: eight registers that hold the constant for the write-back stores.
+    [[maybe_unused]] uint32_t m8[8];
+    if constexpr (kBias) {
+        // Every partial buffer starts out holding the constant in all 128 lanes x 512 columns.
+        if (warp >= 4) {
+            uint32_t init8[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) init8[j] = kMagicBits;
+            const uint32_t base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) + static_cast<uint32_t>(((warp - 4) >> 2) * 128);
+#pragma unroll 1
+            for (int c = 0; c < 128; c += 8) tmem_st_32x32b_x8(base + c, init8);
+            tmem_st_wait();
+            // Read the constant back (before any MMA can run): a tensor-memory load leaves its eight results in
+            // consecutive registers, which is what the stores in the K loop want as their source -- with eight
+            // independently defined registers the compiler copies them together again for every store.
+            tmem_ld_32x32b_x8(base, m8);
+            tmem_ld_wait();
+        }
+        tcgen05_fence_before_sync();
+        __syncthreads();
+        tcgen05_fence_after_sync();
+    }
 
     if (warp < 4) {
         setmaxnreg_dec<kControlRegs>();
@@ -183,7 +246,9 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     for (int kb = 0; kb < num_kb; ++kb, ++it) {
                         const uint32_t s = it % STAGES;
                         const uint32_t ph = (it / STAGES) & 1;
-                        if (!wait_or_abort(&bar_done[s], ph ^ 1, &abort_flag)) {
+                        bool freed = wait_or_abort(&bar_done[0][s], ph ^ 1, &abort_flag);
+                        if (SPLIT == 2 && freed) freed = wait_or_abort(&bar_done[SPLIT - 1][s], ph ^ 1, &abort_flag);
+                        if (!freed) {
                             raise_error(p.status, &abort_flag, ERR_TIMEOUT_PRODUCER);
                             ok = false;
                             break;
@@ -221,28 +286,42 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     const uint32_t ph = (it / STAGES) & 1;
                     const uint32_t buf = it % NBUF;
                     const uint32_t bph = (it / NBUF) & 1;
-                    const long long c0 = clock64();
-                    const bool w1 = wait_or_abort(&bar_part_empty[buf], bph ^ 1, &abort_flag);
-                    const long long c1 = clock64();
-                    if (!w1 || !wait_or_abort(&bar_full[s], ph, &abort_flag)) {
-                        raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
-                        break;
-                    }
-                    const long long c2 = clock64();
-                    tcgen05_fence_after_sync();
+                    // The operands first (they land long before the partial buffer is free) and everything that
+                    // can be prepared, so that nothing but the MMAs stands between the buffer hand-back and the
+                    // tensor core.
+                    [[maybe_unused]] const long long c0 = GI8_BW_CLOCK();
+                    const bool w1 = wait_or_abort(&bar_full[s], ph, &abort_flag);
                     const uint32_t tmem_d = tmem_base + buf * BN;
                     const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
                     const uint64_t da = make_smem_desc_k128(a_addr);
                     const uint64_t db = make_smem_desc_k128(a_addr + kBytesA);
+                    [[maybe_unused]] const long long c1 = GI8_BW_CLOCK();
+                    [[maybe_unused]] long long c2 = 0, c3 = 0;
+                    bool issued = w1;
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k)
-                        umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, k != 0 ? 1u : 0u);
-                    const long long c3 = clock64();
-                    umma_commit(&bar_done[s]);
-                    GI8_BW_DBG(0, c1 - c0);
-                    GI8_BW_DBG(1, c2 - c1);
+                    for (int h = 0; h < SPLIT && issued; ++h) {
+                        if (!wait_or_abort(&bar_part_empty[h][buf], bph ^ 1, &abort_flag)) {
+                            issued = false;
+                            break;
+                        }
+                        if (h == 0) c2 = GI8_BW_CLOCK();
+                        tcgen05_fence_after_sync();
+                        // Half h: rows h * NSUB.. of the weight tile (NSUB rows of 128 bytes: 16-byte units in
+                        // the descriptor's address field) into columns h * NSUB.. of the partial buffer.
+#pragma unroll
+                        for (int k = 0; k < kBK / kUmmaK; ++k)
+                            umma_i8(tmem_d + h * NSUB, da + 2 * k, db + (h * NSUB * kBK) / 16 + 2 * k, kIdesc, (kBias || k != 0) ? 1u : 0u);
+                        if (h == SPLIT - 1) c3 = GI8_BW_CLOCK();
+                        umma_commit(&bar_done[h][s]);
+                    }
+                    if (!issued) {
+                        raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
+                        break;
+                    }
+                    GI8_BW_DBG(1, c1 - c0);
+                    GI8_BW_DBG(0, c2 - c1);
                     GI8_BW_DBG(2, c3 - c2);
-                    GI8_BW_DBG(3, clock64() - c3);
+                    GI8_BW_DBG(3, GI8_BW_CLOCK() - c3);
                     GI8_BW_DBG(4, 1);
                 }
             }
@@ -251,21 +330,65 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         // ------------------------------------------------------------------ promotion + epilogue warps
         setmaxnreg_inc<kPromoRegs>();
         const int quarter = warp & 3;
-        const int cg = (warp - 4) >> 2;
-        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        constexpr int kChunk = 16;          // columns per tensor-memory load
-        constexpr int NC = CW / kChunk;     // chunks per K block per warp (4 or 2, even)
-        static_assert(NC % 2 == 0, "the two chunk registers alternate statically");
+        const int cg = (warp - 4) >> 2;   // column quarter of the tile
+        // Tensor-memory address of this warp's lanes and first column in partial buffer 0 (buffer b is b * BN
+        // columns further).  GI8_PIN keeps such loop-invariant values in a register: left alone, the compiler
+        // re-derives them from %tid.x inside the K loop -- a dozen integer instructions per use, in a loop whose
+        // bound is instruction issue.
+        uint32_t tm_warp = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(cg * CW);
+        GI8_PIN(tm_warp);
+        // Barriers of this warp's column half, as shared-memory addresses.
+        const int half = SPLIT == 2 ? cg >> 1 : 0;
+        uint32_t bar_done_h = smem_u32(&bar_done[half][0]);
+        uint32_t bar_empty_h = smem_u32(&bar_part_empty[half][0]);
+        if constexpr (SPLIT == 2) {
+            GI8_PIN(bar_done_h);
+            GI8_PIN(bar_empty_h);
+        }
+        // How a warp's CW columns of a K block travel from tensor memory to registers:
+        //   PIPE_X16_DOUBLE  16-column loads into two alternating register sets; while one set is converted the
+        //                    next load (the first of the next K block after the last) is in flight.
+        //   PIPE_X32_DOUBLE  the same with 32-column loads (needs CW == 32: 32 accumulators + 2 x 32 registers).
+        //   PIPE_X32_SINGLE  32-column loads into one register set, load -> wait -> convert; the latency is
+        //                    covered by the other warps of the scheduler only.
+        constexpr int kChunk = (PIPE == PIPE_X16_DOUBLE || PIPE == PIPE_X16_SINGLE) ? 16 : 32;  // columns per load
+        constexpr bool kDouble = PIPE == PIPE_X16_DOUBLE || PIPE == PIPE_X32_DOUBLE;
+        constexpr int NC = CW / kChunk;                             // chunks per K block per warp
+        static_assert(CW % kChunk == 0 && (!kDouble || NC == 1 || NC % 2 == 0), "chunk registers alternate statically");
         uint32_t it = 0;                    // running K-block counter, as in the MMA warp
         bool ok = true;
 
-        // Software pipeline over 16-column chunks that runs ACROSS K blocks: while chunk c is converted and
-        // accumulated, the load of the next chunk -- the first chunk of the next K block when c is the last --
-        // is already in flight, so neither the tensor-memory load latency nor the hand-over to the MMA warp sits
-        // in front of the arithmetic.  A buffer is handed back as soon as its last chunk is in registers.
-        uint32_t va[kChunk], vb[kChunk];
-        long long dbg_t = clock64();
+        uint32_t va[kChunk], vb[kDouble ? kChunk : 1];
+
+        [[maybe_unused]] long long dbg_t = GI8_BW_CLOCK();
         const int first_tile = blockIdx.x;
+
+        auto load_chunk = [&](uint32_t taddr, uint32_t (&v)[kChunk]) {
+            if constexpr (kChunk == 16) tmem_ld_32x32b_x16(taddr, v);
+            else tmem_ld_32x32b_x32(taddr, v);
+        };
+        // Waits for the partial of K block `kblock` (running index); false on every lane if any lane gave up.
+        // The common case is one successful test; the branch to the bounded spin is taken on a vote, which makes
+        // it warp-uniform (no reconvergence bookkeeping in the loop).
+        auto wait_partial = [&](uint32_t kblock) {
+            const uint32_t bar = bar_done_h + (kblock % STAGES) * 8;
+            const uint32_t parity = (kblock / STAGES) & 1;
+            bool got = mbar_try_wait_addr(bar, parity);
+            if (!__all_sync(0xffffffffu, got)) {
+                got = wait_or_abort_addr(bar, parity, &abort_flag);
+                if (!got && lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
+                got = __all_sync(0xffffffffu, got);
+                if (!got) return false;
+            }
+            tcgen05_fence_after_sync();
+            return true;
+        };
+        // The whole partial buffer of K block `kblock` is in registers: hand it back to the MMA issuers.
+        auto release_partial = [&](uint32_t kblock) {
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            mbar_arrive_elected_addr(bar_empty_h + (kblock % NBUF) * 8);
+        };
 
         for (int tile = first_tile; tile < num_tiles && ok; tile += gridDim.x) {
             int mb, nb;
@@ -275,109 +398,147 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             const int col_base = nb * BN + cg * CW;  // first output column of this warp
             // A column quarter lies inside one 128-wide weight-scale block (CW divides 128, col_base % CW == 0).
             const bool cols_ok = col_base < p.N;
-            const float* sa_row = p.sa + static_cast<int64_t>(row_ok ? row : 0) * p.ld_sa;
-            const float* sw_row = p.sw + static_cast<int64_t>(cols_ok ? col_base / 128 : 0) * p.ld_sw;
+            // 32-bit element offsets (the scale arrays are far smaller than 2^31 elements) instead of two pointers.
+            uint32_t sa_off = static_cast<uint32_t>(row_ok ? row : 0) * static_cast<uint32_t>(p.ld_sa);
+            uint32_t sw_off = static_cast<uint32_t>(cols_ok ? col_base / 128 : 0) * static_cast<uint32_t>(p.ld_sw);
+            GI8_PIN(sa_off);
+            GI8_PIN(sw_off);
 
-            // First chunk of the tile's first K block (not issued from the previous tile's last chunk: the
-            // epilogue then runs without a chunk in flight, which it has no registers for).
-            if (!wait_or_abort(&bar_done[it % STAGES], (it / STAGES) & 1, &abort_flag)) {
-                if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
+            // The tile's first K block (no load is carried over from the previous tile: the epilogue then runs
+            // without a chunk in flight, which it has no registers for).
+            if (!wait_partial(it)) {
                 ok = false;
+                break;
             }
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tcgen05_fence_after_sync();
-            tmem_ld_32x32b_x16(tmem_base + lane_base + (it % NBUF) * BN + cg * CW, va);
+            if constexpr (kDouble) load_chunk(tm_warp + (it % NBUF) * BN, va);
 
             float acc[CW];
 #pragma unroll
             for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
 
-            float sa_next = __ldg(sa_row);
-            float sw_next = __ldg(sw_row);
-            tmem_ld_wait();
-            for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                float t = sa_next * sw_next;  // fp32, round to nearest: the scale of this K block
+            float sa_next = __ldg(p.sa + sa_off);
+            float sw_next = __ldg(p.sw + sw_off);
+            if constexpr (kDouble) tmem_ld_wait();
+
+            float t = 0.0f;
+            // Scale of K block kb (fp32 product, round to nearest) and the loads for the next one.
+            auto next_scale = [&](int kb) {
+                t = sa_next * sw_next;
                 if constexpr (PROMO == PROMO_ABLATE_SCALES) t = 0.5f;
                 if (PROMO != PROMO_ABLATE_SCALES && kb + 1 < num_kb) {
-                    sa_next = __ldg(sa_row + kb + 1);
-                    sw_next = __ldg(sw_row + kb + 1);
+                    sa_next = __ldg(p.sa + (sa_off + kb + 1));
+                    sw_next = __ldg(p.sw + (sw_off + kb + 1));
                 }
-                const uint32_t taddr = tmem_base + lane_base + (it % NBUF) * BN + cg * CW;
-
-                auto consume = [&](const uint32_t (&v)[kChunk], int c) {
-                    if constexpr (PROMO == PROMO_ABLATE_HANDSHAKE) return;
-                    if constexpr (PROMO == PROMO_ABLATE_LOAD) {
-                        acc[c] = __uint_as_float(__float_as_uint(acc[c]) ^ v[0] ^ v[kChunk - 1]);
-                        return;
-                    }
-                    if constexpr (PROMO == PROMO_ABLATE_MATH) {
-                        acc[c] = __uint_as_float(__float_as_uint(acc[c]) ^ v[0] ^ v[kChunk - 1]) + t;
-                        return;
-                    }
+            };
+            auto consume = [&](const uint32_t (&v)[kChunk], int c) {
+                if constexpr (PROMO == PROMO_ABLATE_HANDSHAKE) return;
+                if constexpr (PROMO == PROMO_ABLATE_LOAD) {
+                    acc[c] = __uint_as_float(__float_as_uint(acc[c]) ^ v[0] ^ v[kChunk - 1]);
+                    return;
+                }
+                if constexpr (PROMO == PROMO_ABLATE_MATH) {
+                    acc[c] = __uint_as_float(__float_as_uint(acc[c]) ^ v[0] ^ v[kChunk - 1]) + t;
+                    return;
+                }
 #pragma unroll
-                    for (int j = 0; j < kChunk; j += 2) {
-                        if constexpr (PROMO == PROMO_ABLATE_FMA_ONLY) {
-                            acc[c + j] = fmaf(__uint_as_float(v[j]), t, acc[c + j]);
-                            acc[c + j + 1] = fmaf(__uint_as_float(v[j + 1]), t, acc[c + j + 1]);
-                        } else if constexpr (PROMO == PROMO_ABLATE_CVT_ONLY) {
-                            acc[c + j] = __int2float_rn(static_cast<int32_t>(v[j]) + __float_as_int(acc[c + j]));
-                            acc[c + j + 1] = __int2float_rn(static_cast<int32_t>(v[j + 1]) + __float_as_int(acc[c + j + 1]));
-                        } else if constexpr (kPacked) {
-                            const uint64_t neg2 = pack_f32x2(__float_as_uint(-kMagicF32), __float_as_uint(-kMagicF32));
-                            const uint64_t t2 = pack_f32x2(__float_as_uint(t), __float_as_uint(t));
-                            const uint64_t pf = add_f32x2(pack_f32x2(v[j] + kMagicBits, v[j + 1] + kMagicBits), neg2);
-                            const uint64_t a2 = fma_f32x2(
-                                pf, t2, pack_f32x2(__float_as_uint(acc[c + j]), __float_as_uint(acc[c + j + 1])));
-                            unpack_f32x2(a2, acc[c + j], acc[c + j + 1]);
-                        } else if constexpr (PROMO == PROMO_I2F || PROMO == PROMO_ABLATE_SCALES) {
-                            acc[c + j] = fmaf(__int2float_rn(static_cast<int32_t>(v[j])), t, acc[c + j]);
-                            acc[c + j + 1] = fmaf(__int2float_rn(static_cast<int32_t>(v[j + 1])), t, acc[c + j + 1]);
-                        } else {
-                            acc[c + j] = fmaf(__uint_as_float(v[j] + kMagicBits) - kMagicF32, t, acc[c + j]);
-                            acc[c + j + 1] = fmaf(__uint_as_float(v[j + 1] + kMagicBits) - kMagicF32, t, acc[c + j + 1]);
-                        }
-                    }
-                };
-
-#pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    // Chunk c of this K block is in va (c even) or vb (c odd) and has landed.
-                    bool in_flight = false;
-                    if (c + 1 < NC) {
-                        if (c & 1) tmem_ld_32x32b_x16(taddr + (c + 1) * kChunk, va);
-                        else tmem_ld_32x32b_x16(taddr + (c + 1) * kChunk, vb);
-                        in_flight = true;
+                for (int j = 0; j < kChunk; j += 2) {
+                    if constexpr (PROMO == PROMO_ABLATE_FMA_ONLY) {
+                        acc[c + j] = fmaf(__uint_as_float(v[j]), t, acc[c + j]);
+                        acc[c + j + 1] = fmaf(__uint_as_float(v[j + 1]), t, acc[c + j + 1]);
+                    } else if constexpr (PROMO == PROMO_ABLATE_CVT_ONLY) {
+                        acc[c + j] = __int2float_rn(static_cast<int32_t>(v[j]) + __float_as_int(acc[c + j]));
+                        acc[c + j + 1] = __int2float_rn(static_cast<int32_t>(v[j + 1]) + __float_as_int(acc[c + j + 1]));
+                    } else if constexpr (kBias) {
+                        promote_biased_pair(v[j], v[j + 1], t, acc[c + j], acc[c + j + 1]);
+                    } else if constexpr (kPacked) {
+                        const uint64_t neg2 = pack_f32x2(__float_as_uint(-kMagicF32), __float_as_uint(-kMagicF32));
+                        const uint64_t t2 = pack_f32x2(__float_as_uint(t), __float_as_uint(t));
+                        const uint64_t pf = add_f32x2(pack_f32x2(v[j] + kMagicBits, v[j + 1] + kMagicBits), neg2);
+                        const uint64_t a2 = fma_f32x2(
+                            pf, t2, pack_f32x2(__float_as_uint(acc[c + j]), __float_as_uint(acc[c + j + 1])));
+                        unpack_f32x2(a2, acc[c + j], acc[c + j + 1]);
+                    } else if constexpr (PROMO == PROMO_I2F || PROMO == PROMO_ABLATE_SCALES) {
+                        acc[c + j] = fmaf(__int2float_rn(static_cast<int32_t>(v[j])), t, acc[c + j]);
+                        acc[c + j + 1] = fmaf(__int2float_rn(static_cast<int32_t>(v[j + 1])), t, acc[c + j + 1]);
                     } else {
-                        // Last chunk: the whole buffer is in registers -> hand it back, then start on the next
-                        // K block (possibly the next tile's first) before doing this chunk's arithmetic.
-                        tcgen05_fence_before_sync();
-                        __syncwarp();
-                        if (lane == 0) mbar_arrive(&bar_part_empty[it % NBUF]);
-                        const bool have_next = kb + 1 < num_kb;
-                        if (have_next) {
-                            const uint32_t nit = it + 1;
-                            const long long w0 = clock64();
-                            if (warp == 4 && lane == 0) { GI8_BW_DBG(6, w0 - dbg_t); }
-                            if (!wait_or_abort(&bar_done[nit % STAGES], (nit / STAGES) & 1, &abort_flag)) {
-                                if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
-                                ok = false;
-                            }
-                            ok = __all_sync(0xffffffffu, ok);
-                            dbg_t = clock64();
-                            if (warp == 4 && lane == 0) { GI8_BW_DBG(5, dbg_t - w0); GI8_BW_DBG(7, 1); }
-                            if (ok) {
-                                tcgen05_fence_after_sync();
-                                tmem_ld_32x32b_x16(tmem_base + lane_base + (nit % NBUF) * BN + cg * CW, va);
-                                in_flight = true;
-                            }
-                        }
+                        acc[c + j] = fmaf(__uint_as_float(v[j] + kMagicBits) - kMagicF32, t, acc[c + j]);
+                        acc[c + j + 1] = fmaf(__uint_as_float(v[j + 1] + kMagicBits) - kMagicF32, t, acc[c + j + 1]);
                     }
-                    if (c & 1) consume(vb, c * kChunk);
-                    else consume(va, c * kChunk);
-                    if (in_flight) tmem_ld_wait();
                 }
-                if (!ok) break;
+            };
+            // Double-buffered step for the LAST chunk (column offset c) of K block kb, which has landed in `cur`:
+            // hand the buffer back, start on the next K block's first chunk (into `nxt`), then do the arithmetic.
+            auto last_chunk_step = [&](const uint32_t (&cur)[kChunk], uint32_t (&nxt)[kChunk], int kb, int c) {
+                release_partial(it);
+                bool in_flight = false;
+                if (kb + 1 < num_kb) {
+                    [[maybe_unused]] const long long w0 = GI8_BW_CLOCK();
+                    if (warp == 4 && lane == 0) { GI8_BW_DBG(6, w0 - dbg_t); }
+                    ok = wait_partial(it + 1);
+                    dbg_t = GI8_BW_CLOCK();
+                    if (warp == 4 && lane == 0) { GI8_BW_DBG(5, dbg_t - w0); GI8_BW_DBG(7, 1); }
+                    if (ok) {
+                        load_chunk(tm_warp + ((it + 1) % NBUF) * BN, nxt);
+                        in_flight = true;
+                    }
+                }
+                consume(cur, c);
+                if (in_flight) tmem_ld_wait();
+            };
+
+            if constexpr (!kDouble) {
+                for (int kb = 0;;) {
+                    next_scale(kb);
+                    const uint32_t taddr = tm_warp + (it % NBUF) * BN;
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        load_chunk(taddr + c * kChunk, va);
+                        tmem_ld_wait();
+                        if constexpr (kBias) {
+#pragma unroll
+                            for (int j = 0; j < kChunk; j += 8) tmem_st_32x32b_x8(taddr + c * kChunk + j, m8);
+                            if (c + 1 == NC) tmem_st_wait();
+                        }
+                        if (c + 1 == NC) release_partial(it);
+                        consume(va, c * kChunk);
+                    }
+                    ++it;
+                    if (++kb == num_kb) break;
+                    if (!wait_partial(it)) {
+                        ok = false;
+                        break;
+                    }
+                }
+            } else if constexpr (NC == 1) {
+                // One chunk per K block: the register sets alternate from K block to K block.
+                for (int kb = 0; kb < num_kb && ok; kb += 2) {
+                    next_scale(kb);
+                    last_chunk_step(va, vb, kb, 0);
+                    ++it;
+                    if (kb + 1 < num_kb && ok) {
+                        next_scale(kb + 1);
+                        last_chunk_step(vb, va, kb + 1, 0);
+                        ++it;
+                    }
+                }
+            } else {
+                for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
+                    next_scale(kb);
+                    const uint32_t taddr = tm_warp + (it % NBUF) * BN;
+#pragma unroll
+                    for (int c = 0; c + 1 < NC; ++c) {
+                        // Chunk c is in va (c even) or vb (c odd) and has landed; chunk c + 1 goes to the other set.
+                        if (c & 1) {
+                            load_chunk(taddr + (c + 1) * kChunk, va);
+                            consume(vb, c * kChunk);
+                        } else {
+                            load_chunk(taddr + (c + 1) * kChunk, vb);
+                            consume(va, c * kChunk);
+                        }
+                        tmem_ld_wait();
+                    }
+                    last_chunk_step(vb, va, kb, (NC - 1) * kChunk);  // NC is even: the last chunk is in vb
+                }
             }
             if (!ok) break;
 

@@ -69,13 +69,26 @@ GI8_DEVICE void mbar_arrive(uint64_t* bar)
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// One elected lane of the (converged) warp arrives; predicated, so no branch.  `bar_addr` is a shared-memory address.
+GI8_DEVICE void mbar_arrive_elected_addr(uint32_t bar_addr)
+{
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "elect.sync _|p, 0xffffffff;\n\t"
+        "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t"
+        "}\n" ::"r"(bar_addr)
+        : "memory");
+}
+
 GI8_DEVICE void mbar_arrive_expect_tx(uint64_t* bar, uint32_t tx_bytes)
 {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(tx_bytes)
                  : "memory");
 }
 
-GI8_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity)
+// `bar_addr` is a shared-memory address.
+GI8_DEVICE bool mbar_try_wait_addr(uint32_t bar_addr, uint32_t parity)
 {
     uint32_t ok;
     asm volatile(
@@ -85,10 +98,12 @@ GI8_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity)
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(bar_addr), "r"(parity)
         : "memory");
     return ok != 0;
 }
+
+GI8_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) { return mbar_try_wait_addr(smem_u32(bar), parity); }
 
 // try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or about
 // `hint_ns` nanoseconds pass, instead of burning issue slots that working warps on the same scheduler need.
@@ -313,6 +328,17 @@ GI8_DEVICE void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
         : "r"(taddr)
         : "memory");
 }
+
+// tcgen05.st: registers -> TMEM, same addressing as the loads.  The source registers are read asynchronously:
+// they must keep their value until tmem_st_wait().
+GI8_DEVICE void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t (&r)[8])
+{
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
+                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+
+GI8_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 GI8_DEVICE void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
 {

@@ -240,10 +240,13 @@ def test_blockwise_edge_shapes(g, oracle, variant):
     g.force_variant(None)
 
 
-@pytest.mark.parametrize("promotion", ["0", "1", "2"])
-def test_blockwise_promotion_modes_agree(g, oracle, promotion, monkeypatch):
-    """The three promotion arithmetics (scalar magic-number, packed, TMEM-biased packed) are bit-identical."""
+@pytest.mark.parametrize("halves", ["1", "2"])
+@pytest.mark.parametrize("promotion", ["0", "1", "2", "9"])
+def test_blockwise_promotion_modes_agree(g, oracle, promotion, halves, monkeypatch):
+    """The promotion arithmetics (scalar magic-number, packed, cvt + fma, biased accumulator) and the two MMA
+    shapes of the 256-wide tile are bit-identical."""
     monkeypatch.setenv("GEMM_INT8_PROMOTION", promotion)
+    monkeypatch.setenv("GEMM_INT8_HALVES", halves)
     gen = torch.Generator().manual_seed(52)
     for variant in ("dense_bn128", "dense_bn256", "pair"):
         g.force_variant(variant)
