@@ -133,16 +133,16 @@ int check_common(const void* x, const void* y, const void* out, int64_t M, int64
 // Dispatch: picks the tile width for the dense/blockwise kernels.  Model fitted on B200: the grid runs
 // ceil(tiles / SMs) waves; a wave of 128 x BN tiles costs BN x c(BN) + a fixed part per K block, where c is the
 // measured inefficiency of the narrower tensor-core instruction (its shared-memory operand traffic per MAC is
-// higher): dense 2900 / 1750 / 1000 TOP/s at BN = 256 / 128 / 64, blockwise 1550 / 1400 at BN = 256 / 128.
+// higher): dense 2900 / 1750 / 1000 TOP/s and blockwise 1900 / 1520 / 850 TOP/s at BN = 256 / 128 / 64.
 // ---------------------------------------------------------------------------------------------------
 int pick_bn(int64_t M, int64_t N, int sms, bool blockwise)
 {
     const int cand[3] = {256, 128, 64};
     const double ineff_dense[3] = {1.0, 1.65, 2.9};
-    const double ineff_block[3] = {1.0, 1.12, 0.0};
+    const double ineff_block[3] = {1.0, 1.35, 2.4};
     int best = 256;
     double best_cost = 1e300;
-    for (int i = 0; i < (blockwise ? 2 : 3); ++i) {
+    for (int i = 0; i < 3; ++i) {
         const int bn = cand[i];
         const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
         const int64_t waves = (tiles + sms - 1) / sms;
@@ -677,6 +677,7 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     switch (g_forced_variant) {
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
+        case VAR_DENSE_BN64: bn = 64; break;
         default: bn = pick_bn(M, N, st->sm_count, true);
     }
     p.tiles_m = (int)((M + kBM - 1) / kBM);
@@ -697,11 +698,12 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     // Tuning knobs (not part of the ABI; every combination gives bit-identical results):
     //   GEMM_INT8_PROMOTION = 0 | 1 | 2 | 9   promotion arithmetic (default 9, the biased accumulator; 3..8 are
     //                                         measurement-only ablations with wrong results, tuning builds only)
-    //   GEMM_INT8_PIPE      = 0 | 2           with promotion 2: double-buffered 16-column or single 32-column loads
+    //   GEMM_INT8_PIPE      = 0 | 2           with promotion 2: double-buffered 16-column (default) or single
+    //                                         32-column loads
     //   GEMM_INT8_HALVES    = 1 | 2           256-wide tile: MMAs with N = 256, or two column halves with N = 128
     int promo = PROMO_BIAS_X2;
     if (const char* e = getenv("GEMM_INT8_PROMOTION")) promo = atoi(e);
-    int pipe = bn == 256 ? PIPE_X32_SINGLE : PIPE_X16_DOUBLE;
+    int pipe = -1;
     if (const char* e = getenv("GEMM_INT8_PIPE")) pipe = atoi(e);
     int split = 2;
     if (const char* e = getenv("GEMM_INT8_HALVES")) split = atoi(e) == 1 ? 1 : 2;
@@ -734,6 +736,9 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
         else if (promo == PROMO_I2F) GI8_LAUNCH_BW(256, 4, PROMO_I2F, 17);
         else if (split == 2) GI8_LAUNCH_BWP(256, 4, PROMO_BIAS_X2, PIPE_X16_SINGLE, 2, 38);
         else GI8_LAUNCH_BWP(256, 4, PROMO_BIAS_X2, PIPE_X16_SINGLE, 1, 39);
+    } else if (bn == 64) {
+        // Narrow tile for few-row problems: always the biased accumulator, one 16-column load per K block.
+        GI8_LAUNCH_BWP(64, 8, PROMO_BIAS_X2, PIPE_X16_SINGLE, 1, 41);
     } else {
         if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC, 18);
         else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC_X2, 19);

@@ -156,14 +156,15 @@ __global__ void __launch_bounds__(kBlockwiseThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                       const __grid_constant__ CUtensorMap map_out, const BlockwiseParams p)
 {
-    static_assert(BN == 128 || BN == 256, "BN must be 128 or 256");
+    static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
     static_assert(SPLIT == 1 || (SPLIT == 2 && BN == 256), "column halves only for the 256-wide tile");
-    constexpr int NBUF = 512 / BN;  // partial buffers in tensor memory (2 or 4)
+    constexpr int NBUF = 512 / BN;  // partial buffers in tensor memory (2, 4 or 8)
     constexpr int NSUB = BN / SPLIT;  // N of one MMA
-    constexpr int CW = BN / 4;      // columns per promotion warp (64 or 32)
+    constexpr int CW = BN / 4;      // columns per promotion warp (64, 32 or 16)
     constexpr bool kPacked = PROMO == PROMO_MAGIC_X2;
     constexpr bool kBias = PROMO == PROMO_BIAS_X2;
-    static_assert(!kBias || PIPE == PIPE_X16_SINGLE || PIPE == PIPE_X32_SINGLE, "the constant is written back behind single-buffered loads");
+    // (With double-buffered loads the biased mode works but spills: the write-back stores at several places make
+    // the compiler copy the constant registers.)
     constexpr uint32_t kBytesA = kBM * kBK;
     constexpr uint32_t kBytesB = BN * kBK;
     constexpr uint32_t kStageBytes = kBytesA + kBytesB;
@@ -411,23 +412,39 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 break;
             }
             if constexpr (kDouble) load_chunk(tm_warp + (it % NBUF) * BN, va);
+            [[maybe_unused]] auto store_magic = [&](uint32_t taddr) {
+#pragma unroll
+                for (int jj = 0; jj < kChunk; jj += 8) tmem_st_32x32b_x8(taddr + jj, m8);
+            };
 
             float acc[CW];
 #pragma unroll
             for (int j = 0; j < CW; ++j) acc[j] = 0.0f;
 
-            float sa_next = __ldg(p.sa + sa_off);
-            float sw_next = __ldg(p.sw + sw_off);
-            if constexpr (kDouble) tmem_ld_wait();
+            // Scales are loaded kScaleDepth K blocks before their use (an L2 hit takes longer than one K block);
+            // set j serves the K blocks with kb % kScaleDepth == j, statically, through unrolling.
+            constexpr int kScaleDepth = (kDouble && NC > 1) ? 1 : (BN == 256 ? 2 : (kDouble ? 2 : 4));
+            float sa_q[kScaleDepth], sw_q[kScaleDepth];
+#pragma unroll
+            for (int j = 0; j < kScaleDepth; ++j) {
+                if (j < num_kb) {
+                    sa_q[j] = __ldg(p.sa + (sa_off + j));
+                    sw_q[j] = __ldg(p.sw + (sw_off + j));
+                }
+            }
+            if constexpr (kDouble) {
+                tmem_ld_wait();
+                if constexpr (kBias) store_magic(tm_warp + (it % NBUF) * BN);
+            }
 
             float t = 0.0f;
             // Scale of K block kb (fp32 product, round to nearest) and the loads for the next one.
-            auto next_scale = [&](int kb) {
-                t = sa_next * sw_next;
+            auto scale_from_set = [&](int kb, int j) {
+                t = sa_q[j] * sw_q[j];
                 if constexpr (PROMO == PROMO_ABLATE_SCALES) t = 0.5f;
-                if (PROMO != PROMO_ABLATE_SCALES && kb + 1 < num_kb) {
-                    sa_next = __ldg(p.sa + (sa_off + kb + 1));
-                    sw_next = __ldg(p.sw + (sw_off + kb + 1));
+                if (PROMO != PROMO_ABLATE_SCALES && kb + kScaleDepth < num_kb) {
+                    sa_q[j] = __ldg(p.sa + (sa_off + kb + kScaleDepth));
+                    sw_q[j] = __ldg(p.sw + (sw_off + kb + kScaleDepth));
                 }
             };
             auto consume = [&](const uint32_t (&v)[kChunk], int c) {
@@ -466,121 +483,136 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     }
                 }
             };
-            // Double-buffered step for the LAST chunk (column offset c) of K block kb, which has landed in `cur`:
-            // hand the buffer back, start on the next K block's first chunk (into `nxt`), then do the arithmetic.
-            auto last_chunk_step = [&](const uint32_t (&cur)[kChunk], uint32_t (&nxt)[kChunk], int kb, int c) {
-                release_partial(it);
-                bool in_flight = false;
-                if (kb + 1 < num_kb) {
+            // Double-buffered step: chunk c of K block kb has landed in `cur` (and, in the biased mode, the
+            // constant has been written back over it).  Start the next chunk's load into `nxt` -- the first chunk
+            // of the next K block after the last one -- then do this chunk's arithmetic; the buffer is handed
+            // back after the last chunk's arithmetic, when the write-back stores have long completed.
+            auto chunk_step = [&](const uint32_t (&cur)[kChunk], uint32_t (&nxt)[kChunk], int kb, int c) {
+                const bool last_chunk = c + 1 == NC;
+                const bool have_next = !last_chunk || kb + 1 < num_kb;
+                uint32_t next_addr = tm_warp + (it % NBUF) * BN + (c + 1) * kChunk;
+                if (last_chunk && have_next) {
                     [[maybe_unused]] const long long w0 = GI8_BW_CLOCK();
                     if (warp == 4 && lane == 0) { GI8_BW_DBG(6, w0 - dbg_t); }
                     ok = wait_partial(it + 1);
                     dbg_t = GI8_BW_CLOCK();
                     if (warp == 4 && lane == 0) { GI8_BW_DBG(5, dbg_t - w0); GI8_BW_DBG(7, 1); }
-                    if (ok) {
-                        load_chunk(tm_warp + ((it + 1) % NBUF) * BN, nxt);
-                        in_flight = true;
-                    }
+                    next_addr = tm_warp + ((it + 1) % NBUF) * BN;
                 }
-                consume(cur, c);
-                if (in_flight) tmem_ld_wait();
+                const bool in_flight = have_next && ok;
+                if (in_flight) load_chunk(next_addr, nxt);
+                consume(cur, c * kChunk);
+                if (last_chunk) {
+                    if constexpr (kBias) tmem_st_wait();
+                    release_partial(it);
+                    ++it;
+                }
+                if (in_flight) {
+                    tmem_ld_wait();
+                    if constexpr (kBias) store_magic(next_addr);
+                }
             };
 
             if constexpr (!kDouble) {
-                for (int kb = 0;;) {
-                    next_scale(kb);
-                    const uint32_t taddr = tm_warp + (it % NBUF) * BN;
+                bool tile_done = false;
+                for (int kb = 0; !tile_done && ok;) {
 #pragma unroll
-                    for (int c = 0; c < NC; ++c) {
-                        load_chunk(taddr + c * kChunk, va);
-                        tmem_ld_wait();
-                        if constexpr (kBias) {
+                    for (int j = 0; j < kScaleDepth; ++j) {
+                        scale_from_set(kb, j);
+                        const uint32_t taddr = tm_warp + (it % NBUF) * BN;
 #pragma unroll
-                            for (int j = 0; j < kChunk; j += 8) tmem_st_32x32b_x8(taddr + c * kChunk + j, m8);
-                            if (c + 1 == NC) tmem_st_wait();
+                        for (int c = 0; c < NC; ++c) {
+                            load_chunk(taddr + c * kChunk, va);
+                            tmem_ld_wait();
+                            if constexpr (kBias) {
+#pragma unroll
+                                for (int jj = 0; jj < kChunk; jj += 8) tmem_st_32x32b_x8(taddr + c * kChunk + jj, m8);
+                                if (c + 1 == NC) tmem_st_wait();
+                            }
+                            if (c + 1 == NC) release_partial(it);
+                            consume(va, c * kChunk);
                         }
-                        if (c + 1 == NC) release_partial(it);
-                        consume(va, c * kChunk);
-                    }
-                    ++it;
-                    if (++kb == num_kb) break;
-                    if (!wait_partial(it)) {
-                        ok = false;
-                        break;
+                        ++it;
+                        if (++kb == num_kb) {
+                            tile_done = true;
+                            break;
+                        }
+                        [[maybe_unused]] const long long w0 = GI8_BW_CLOCK();
+                        if (warp == 4 && lane == 0) { GI8_BW_DBG(6, w0 - dbg_t); }
+                        if (!wait_partial(it)) {
+                            ok = false;
+                            break;
+                        }
+                        dbg_t = GI8_BW_CLOCK();
+                        if (warp == 4 && lane == 0) { GI8_BW_DBG(5, dbg_t - w0); GI8_BW_DBG(7, 1); }
                     }
                 }
             } else if constexpr (NC == 1) {
-                // One chunk per K block: the register sets alternate from K block to K block.
+                // One chunk per K block: the register sets (and the scale sets) alternate from K block to K block.
                 for (int kb = 0; kb < num_kb && ok; kb += 2) {
-                    next_scale(kb);
-                    last_chunk_step(va, vb, kb, 0);
-                    ++it;
+                    scale_from_set(kb, 0);
+                    chunk_step(va, vb, kb, 0);
                     if (kb + 1 < num_kb && ok) {
-                        next_scale(kb + 1);
-                        last_chunk_step(vb, va, kb + 1, 0);
-                        ++it;
+                        scale_from_set(kb + 1, 1);
+                        chunk_step(vb, va, kb + 1, 0);
                     }
                 }
             } else {
-                for (int kb = 0; kb < num_kb && ok; ++kb, ++it) {
-                    next_scale(kb);
-                    const uint32_t taddr = tm_warp + (it % NBUF) * BN;
+                for (int kb = 0; kb < num_kb && ok; ++kb) {
+                    scale_from_set(kb, 0);
 #pragma unroll
-                    for (int c = 0; c + 1 < NC; ++c) {
-                        // Chunk c is in va (c even) or vb (c odd) and has landed; chunk c + 1 goes to the other set.
-                        if (c & 1) {
-                            load_chunk(taddr + (c + 1) * kChunk, va);
-                            consume(vb, c * kChunk);
-                        } else {
-                            load_chunk(taddr + (c + 1) * kChunk, vb);
-                            consume(va, c * kChunk);
-                        }
-                        tmem_ld_wait();
+                    for (int c = 0; c < NC; c += 2) {
+                        chunk_step(va, vb, kb, c);  // NC is even: even chunks in va, odd chunks in vb
+                        chunk_step(vb, va, kb, c + 1);
                     }
-                    last_chunk_step(vb, va, kb, (NC - 1) * kChunk);  // NC is even: the last chunk is in vb
                 }
             }
             if (!ok) break;
 
-            if (p.tma_store) {
-                // 32 x 32 blocks through 64-byte-swizzled shared memory and TMA stores (rows >= M and columns >= N
-                // are clipped by the hardware); see the dense kernel's epilogue for the layout.  The tile's
-                // coordinates are derived again from an opaque copy of the tile index so that they do not occupy
-                // registers across the promotion loop.
-                int tile_again = tile, mb2, nb2;
-                asm volatile("" : "+r"(tile_again));
-                tile_coords(tile_again, p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
-                const int row0 = mb2 * kBM + quarter * 32;
-                const int col_base = nb2 * BN + cg * CW;
-                if (row0 < p.M && col_base < p.N) {
-                    const uint32_t stg = ((smem_u32(smem_raw) + 1023u) & ~1023u) + STAGES * kStageBytes + (warp - 4) * 2048;
+            bool stored = false;
+            if constexpr (CW >= 32) {
+                if (p.tma_store) {
+                    stored = true;
+                    // 32 x 32 blocks through 64-byte-swizzled shared memory and TMA stores (rows >= M and columns >= N
+                    // are clipped by the hardware); see the dense kernel's epilogue for the layout.  The tile's
+                    // coordinates are derived again from an opaque copy of the tile index so that they do not occupy
+                    // registers across the promotion loop.
+                    int tile_again = tile, mb2, nb2;
+                    asm volatile("" : "+r"(tile_again));
+                    tile_coords(tile_again, p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
+                    const int row0 = mb2 * kBM + quarter * 32;
+                    const int col_base = nb2 * BN + cg * CW;
+                    if (row0 < p.M && col_base < p.N) {
+                        const uint32_t stg = ((smem_u32(smem_raw) + 1023u) & ~1023u) + STAGES * kStageBytes + (warp - 4) * 2048;
 #pragma unroll
-                    for (int c = 0; c < CW; c += 32) {
-                        if (col_base + c >= p.N) break;
-                        if (lane == 0) tma_store_wait_read<0>();
-                        __syncwarp();
+                        for (int c = 0; c < CW; c += 32) {
+                            if (col_base + c >= p.N) break;
+                            if (lane == 0) tma_store_wait_read<0>();
+                            __syncwarp();
 #pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const int cq = q ^ ((lane >> 1) & 3);
-                            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * 64 + cq * 16),
-                                         "r"(pack_bf16x2(acc[c + 8 * q], acc[c + 8 * q + 1])),
-                                         "r"(pack_bf16x2(acc[c + 8 * q + 2], acc[c + 8 * q + 3])),
-                                         "r"(pack_bf16x2(acc[c + 8 * q + 4], acc[c + 8 * q + 5])),
-                                         "r"(pack_bf16x2(acc[c + 8 * q + 6], acc[c + 8 * q + 7]))
-                                         : "memory");
-                        }
-                        fence_proxy_async_smem();
-                        __syncwarp();
-                        if (lane == 0) {
-                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                                             reinterpret_cast<uint64_t>(&map_out)),
-                                         "r"(stg), "r"(col_base + c), "r"(row0)
-                                         : "memory");
-                            tma_store_commit();
+                            for (int q = 0; q < 4; ++q) {
+                                const int cq = q ^ ((lane >> 1) & 3);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * 64 + cq * 16),
+                                             "r"(pack_bf16x2(acc[c + 8 * q], acc[c + 8 * q + 1])),
+                                             "r"(pack_bf16x2(acc[c + 8 * q + 2], acc[c + 8 * q + 3])),
+                                             "r"(pack_bf16x2(acc[c + 8 * q + 4], acc[c + 8 * q + 5])),
+                                             "r"(pack_bf16x2(acc[c + 8 * q + 6], acc[c + 8 * q + 7]))
+                                             : "memory");
+                            }
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                                 reinterpret_cast<uint64_t>(&map_out)),
+                                             "r"(stg), "r"(col_base + c), "r"(row0)
+                                             : "memory");
+                                tma_store_commit();
+                            }
                         }
                     }
                 }
-            } else if (row_ok && cols_ok) {
+            }
+            if (!stored && row_ok && cols_ok) {
                 uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col_base;
                 if (col_base + CW <= p.N && p.vec_ok) {
 #pragma unroll

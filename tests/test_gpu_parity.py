@@ -222,7 +222,7 @@ def test_smallm_split_k_scratch_is_left_zeroed(g, oracle):
 
 
 # ---------------------------------------------------------------------------------------- blockwise
-@pytest.mark.parametrize("variant", ["dense_bn128", "dense_bn256", "pair", None])
+@pytest.mark.parametrize("variant", ["dense_bn64", "dense_bn128", "dense_bn256", "pair", None])
 def test_blockwise_edge_shapes(g, oracle, variant):
     g.force_variant(variant)
     gen = torch.Generator().manual_seed(51)
