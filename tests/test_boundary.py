@@ -104,3 +104,17 @@ def test_product_does_not_import_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text.replace("CPU oracle's blockwise restatement", ""), f
+
+
+def test_host_pipeline_rejects_bad_arguments_without_gpu():
+    import torch
+
+    from gemm_int8_b200.host import HostPipeline
+
+    with pytest.raises(ValueError):
+        HostPipeline("nonsense")
+    with pytest.raises(ValueError):
+        HostPipeline("plain", depth=0)
+    if not torch.cuda.is_available():
+        with pytest.raises(RuntimeError):
+            HostPipeline("plain")  # no CPU path

@@ -462,3 +462,33 @@ def test_int8_linear_matches_oracle_pipeline(g, oracle):
 
     compiled = torch.compile(layer, dynamic=True)
     assert torch.equal(compiled(x.cuda()), y)
+
+
+def test_host_pipeline_matches_oracle(g, oracle):
+    """Host-buffer front end: pinned operands in, pinned result out, several calls in flight; every result is
+    bit-identical to the oracle (and so to the device-tensor op)."""
+    from gemm_int8_b200.host import HostPipeline
+
+    gen = torch.Generator().manual_seed(77)
+    pipe = HostPipeline("blockwise", depth=2)
+    cases = []
+    for i, (M, N, K) in enumerate([(130, 264, 400), (64, 512, 1024), (130, 264, 400), (257, 1000, 1040), (1, 8, 16)]):
+        KB, NB = -(-K // 128), -(-N // 128)
+        x, y = rand_i8((M, K), 100 + i), rand_i8((N, K), 200 + i)
+        sa = torch.rand(M, KB, generator=gen) * 0.02 + 1e-3
+        sw = torch.rand(NB, KB, generator=gen) * 0.02 + 1e-3
+        host_in = [t.pin_memory() for t in (x, y, sa, sw)]
+        host_out = torch.empty((M, N), dtype=torch.bfloat16).pin_memory()
+        pipe.submit(host_in, host_out)
+        cases.append((x, y, sa, sw, host_out))
+    pipe.drain()
+    for (x, y, sa, sw, host_out) in cases:
+        assert_bits_equal(oracle, host_out, oracle.c_matmul_blockwise(x, y, sa, sw), "host pipeline")
+    plain = HostPipeline("plain", depth=1)
+    x, y = rand_i8((70, 256), 301), rand_i8((136, 256), 302)
+    out = torch.empty((70, 136), dtype=torch.bfloat16).pin_memory()
+    plain.submit([x.pin_memory(), y.pin_memory()], out)
+    plain.drain()
+    assert_bits_equal(oracle, out, oracle.c_matmul(x, y, 1.0), "host pipeline plain")
+    with pytest.raises(ValueError):
+        plain.submit([x, y.pin_memory()], out)  # not pinned
