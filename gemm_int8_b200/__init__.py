@@ -37,6 +37,7 @@ _libdef.define("int8_matmul_scaled(Tensor A, Tensor B, Tensor a_scale, Tensor b_
 _libdef.define("int8_matmul_blockwise(Tensor A, Tensor B, Tensor A_scale, Tensor B_scale) -> Tensor")
 _libdef.define("quantize_token_block(Tensor a) -> (Tensor, Tensor)")
 _libdef.define("quantize_token(Tensor a) -> (Tensor, Tensor)")
+_libdef.define("hadamard_quantize_token_block(Tensor a, int block) -> (Tensor, Tensor)")
 
 
 def _stream_ptr(device: torch.device) -> ctypes.c_void_p:
@@ -279,12 +280,39 @@ def _quantize(a: torch.Tensor, per_block: bool):
     return q, s
 
 
+def _hadamard_quantize(a: torch.Tensor, block: int):
+    if not a.is_cuda:
+        raise RuntimeError("hadamard_quantize: input must be a CUDA tensor (the torch reference lives in gemm_int8_b200.quant)")
+    if a.dim() != 2:
+        raise RuntimeError("hadamard_quantize: input must be 2-D [tokens, features]")
+    if a.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError(f"hadamard_quantize: input must be float32 or bfloat16, got {a.dtype}")
+    a = a.contiguous()
+    M, K = a.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=a.device)
+    s = torch.empty((M, -(-K // KBLOCK)), dtype=torch.float32, device=a.device)
+    with _on_device(a.device):
+        rc = _C.gi8_hadamard_quantize_token_block(_ptr(a), 0 if a.dtype == torch.float32 else 1, _ptr(q), _ptr(s), M, K,
+                                                  block, _stream_ptr(a.device))
+    _lib.check(_C, rc)
+    return q, s
+
+
+_libdef.impl("hadamard_quantize_token_block", _hadamard_quantize, "CUDA")
 _libdef.impl("quantize_token_block", lambda a: _quantize(a, True), "CUDA")
 _libdef.impl("quantize_token", lambda a: _quantize(a, False), "CUDA")
 
 
 @torch.library.register_fake(f"{_NS}::quantize_token_block")
 def _(a: torch.Tensor):
+    torch._check(len(a.shape) == 2, lambda: "a must be a 2D tensor")
+    kb = (a.shape[1] + KBLOCK - 1) // KBLOCK
+    return (torch.empty(a.shape[0], a.shape[1], device=a.device, dtype=torch.int8),
+            torch.empty(a.shape[0], kb, device=a.device, dtype=torch.float32))
+
+
+@torch.library.register_fake(f"{_NS}::hadamard_quantize_token_block")
+def _(a: torch.Tensor, block: int):
     torch._check(len(a.shape) == 2, lambda: "a must be a 2D tensor")
     kb = (a.shape[1] + KBLOCK - 1) // KBLOCK
     return (torch.empty(a.shape[0], a.shape[1], device=a.device, dtype=torch.int8),
@@ -303,6 +331,17 @@ def quantize_per_token_block(a: torch.Tensor):
     scales fp32 [M, ceil(K/128)]), one symmetric scale per token per 128-wide K block (amax / 127, round half
     even, clamp to +-127) -- bit-identical to `quant.quantize_per_token_block`."""
     return torch.ops.gemm_int8_CUDA.quantize_token_block(a)
+
+
+def hadamard_quantize_per_token_block(a: torch.Tensor, block: int | None = None):
+    """Walsh-Hadamard rotation along K in blocks of `block` (default: the largest power of two dividing K, at most
+    8192) fused with `quantize_per_token_block` in one pass over the activations -- bit-identical to
+    `quant.quantize_per_token_block(quant.hadamard_rotate(a.float(), block))`.  The weights must have been rotated
+    the same way before they were quantised (offline)."""
+    K = a.shape[-1]
+    if block is None:
+        block = min(K & -K, 8192)
+    return torch.ops.gemm_int8_CUDA.hadamard_quantize_token_block(a, block)
 
 
 def quantize_per_token(a: torch.Tensor):

@@ -35,6 +35,7 @@ SYMBOLS = {
     "gi8_matmul_blockwise": (_i, [_p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p]),
     "gi8_quantize_token_block": (_i, [_p, _i, _p, _p, _i64, _i64, _p]),
     "gi8_quantize_token": (_i, [_p, _i, _p, _p, _i64, _i64, _p]),
+    "gi8_hadamard_quantize_token_block": (_i, [_p, _i, _p, _p, _i64, _i64, _i64, _p]),
     "gi8_force_variant": (_i, [ctypes.c_char_p]),
     "gi8_pick_variant": (ctypes.c_char_p, [_i, _i64, _i64, _i64]),
     "gi8_device_status": (_i, [ctypes.POINTER(ctypes.c_uint32)]),

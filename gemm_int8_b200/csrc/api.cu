@@ -366,6 +366,26 @@ int get_static_scratch(void** out)
 
 }  // namespace
 
+template <typename T>
+static int launch_hadamard_quant(const T* in, int8_t* q, float* scales, int64_t M, int K, int KB, int H, cudaStream_t s)
+{
+    const int threads = H / 4 < kQuantThreads ? H / 4 : kQuantThreads;
+    const int e = H / threads;
+    const size_t smem = threads > 32 ? sizeof(float) * H : 0;
+    const float norm = static_cast<float>(pow(static_cast<double>(H), -0.5));
+    const int64_t blocks = M * (K / H);
+    if (blocks > INT32_MAX) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "too many rotation blocks");
+    const int grid = static_cast<int>(blocks);
+    switch (e) {
+        case 4: hadamard_quantize_token_block_kernel<T, 4><<<grid, threads, smem, s>>>(in, q, scales, K, KB, H, norm); break;
+        case 8: hadamard_quantize_token_block_kernel<T, 8><<<grid, threads, smem, s>>>(in, q, scales, K, KB, H, norm); break;
+        case 16: hadamard_quantize_token_block_kernel<T, 16><<<grid, threads, smem, s>>>(in, q, scales, K, KB, H, norm); break;
+        default: hadamard_quantize_token_block_kernel<T, 32><<<grid, threads, smem, s>>>(in, q, scales, K, KB, H, norm); break;
+    }
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
+}
+
 extern "C" {
 
 #ifdef GI8_ENABLE_ABLATIONS
@@ -575,8 +595,8 @@ static int check_quant(const void* in, int in_dtype, const int8_t* q, const floa
     const int64_t mult = in_dtype == 0 ? 4 : 8;
     if (K % mult) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "K=%lld must be a multiple of %lld for this input type",
                               (long long)K, (long long)mult);
-    if (reinterpret_cast<uintptr_t>(in) % 16 || reinterpret_cast<uintptr_t>(q) % 4 || reinterpret_cast<uintptr_t>(scales) % 4)
-        return fail(GI8_ERR_MISALIGNED, "in must be 16-byte aligned, q and scales 4-byte aligned");
+    if (reinterpret_cast<uintptr_t>(in) % 16 || reinterpret_cast<uintptr_t>(q) % 8 || reinterpret_cast<uintptr_t>(scales) % 4)
+        return fail(GI8_ERR_MISALIGNED, "in must be 16-byte aligned, q 8-byte and scales 4-byte aligned");
     return GI8_OK;
 }
 
@@ -588,7 +608,10 @@ int gi8_quantize_token_block(const void* in, int in_dtype, int8_t* q, float* sca
     if (int rc = get_device_state(&st)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int KB = static_cast<int>((K + 127) / 128);
-    const int64_t warps = M * KB;
+    // A warp takes kQuantUnroll loads of 32 lanes x 16 bytes per iteration: 4 (fp32) or 8 (bf16) blocks.
+    const int64_t per_warp = (in_dtype == 0 ? 1 : 2) * kQuantUnroll;
+    const int64_t warps = M * ((KB + per_warp - 1) / per_warp);  // one work item per warp and iteration
+    if (warps >= (int64_t(1) << 32)) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "too many quantisation blocks");
     int64_t blocks = (warps + kQuantThreads / 32 - 1) / (kQuantThreads / 32);
     const int64_t cap = static_cast<int64_t>(st->sm_count) * 16;
     if (blocks > cap) blocks = cap;
@@ -600,6 +623,27 @@ int gi8_quantize_token_block(const void* in, int in_dtype, int8_t* q, float* sca
             static_cast<const __nv_bfloat16*>(in), q, scales, M, static_cast<int>(K), KB);
     GI8_CUDA(cudaGetLastError());
     return GI8_OK;
+}
+
+int gi8_hadamard_quantize_token_block(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K,
+                                      int64_t had_block, void* stream)
+{
+    if (int rc = check_quant(in, in_dtype, q, scales, M, K)) return rc;
+    if (had_block < 128 || had_block > 8192 || (had_block & (had_block - 1)))
+        return fail(GI8_ERR_UNSUPPORTED_SHAPE, "rotation block %lld must be a power of two in [128, 8192]", (long long)had_block);
+    if (K % had_block)
+        return fail(GI8_ERR_UNSUPPORTED_SHAPE, "K=%lld must be a multiple of the rotation block %lld", (long long)K,
+                    (long long)had_block);
+    if (M == 0 || K == 0) return GI8_OK;
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int KB = static_cast<int>(K / 128);
+    if (in_dtype == 0)
+        return launch_hadamard_quant(static_cast<const float*>(in), q, scales, M, static_cast<int>(K), KB,
+                                     static_cast<int>(had_block), s);
+    return launch_hadamard_quant(static_cast<const __nv_bfloat16*>(in), q, scales, M, static_cast<int>(K), KB,
+                                 static_cast<int>(had_block), s);
 }
 
 int gi8_quantize_token(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K, void* stream)

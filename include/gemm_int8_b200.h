@@ -116,12 +116,22 @@ int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, 
  * Activation quantisers that feed the W8A8 entry points (the reference ships none; its benchmark only rounds and
  * clamps, benchmark.py:17-18).  Rule: s = amax / 127 (s = 1 where the block is all zero),
  * q = clamp(round_half_even(v / s), -127, 127).  `in` is row-major [M,K], fp32 (in_dtype 0) or bf16 (in_dtype 1),
- * 16-byte aligned rows (K % 8 == 0 for bf16, K % 4 == 0 for fp32); q int8 [M,K] 4-byte aligned.
+ * 16-byte aligned rows (K % 8 == 0 for bf16, K % 4 == 0 for fp32); q int8 [M,K] 8-byte aligned.
  *   gi8_quantize_token_block : one scale per row per 128-wide K block, scales fp32 [M, ceil(K/128)]
  *   gi8_quantize_token       : one scale per row, scales fp32 [M]
  */
 int gi8_quantize_token_block(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K, void* stream);
 int gi8_quantize_token(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K, void* stream);
+
+/*
+ * gi8_quantize_token_block preceded, in the same kernel, by a normalised Walsh-Hadamard rotation along K in blocks
+ * of `had_block` elements (the rotation the reference's README names as its use case, README.md:10; the reference
+ * has no code for it).  Transform: in-place butterflies with strides 1, 2, 4, ... ascending, (a, b) -> (a + b, a - b)
+ * in fp32, then one multiplication by fp32(had_block^-1/2); then the quantiser's rule per 128-wide block.
+ * had_block: a power of two in [128, 8192] that divides K.  Other arguments as gi8_quantize_token_block.
+ */
+int gi8_hadamard_quantize_token_block(const void* in, int in_dtype, int8_t* q, float* scales, int64_t M, int64_t K,
+                                      int64_t had_block, void* stream);
 
 /*
  * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted

@@ -244,6 +244,31 @@ int gi8o_matmul_blockwise(const int8_t *x, const int8_t *y, const float *sa, int
  * [ceil(R/rb), ceil(C/cb)] row-major.  Used for the synthetic workloads (per-token-per-128-K
  * activation blocks rb=1, cb=128; per-128x128 weight blocks; per-row scales rb=1, cb=C).
  */
+/* Normalised Walsh-Hadamard rotation along each row in blocks of H elements (H a power of two dividing C):
+ * in-place butterflies, strides 1, 2, 4, ... ascending, (a, b) -> (a + b, a - b) in fp32, then one multiplication
+ * by fp32(H^-1/2).  The reference names the rotation as its use case (README.md:10) and has no code for it; this
+ * restates gemm_int8_b200/quant.py:hadamard_rotate.  out may alias in.
+ */
+int gi8o_hadamard_rotate(const float *in, float *out, int64_t R, int64_t C, int64_t H)
+{
+    if (R < 0 || C < 0 || H <= 0 || (H & (H - 1)) || C % H) return GI8O_BAD_ARG;
+    const float norm = (float)pow((double)H, -0.5);
+    for (int64_t r = 0; r < R; ++r)
+        for (int64_t b = 0; b < C; b += H) {
+            float *y = out + r * C + b;
+            if (out != in) memcpy(y, in + r * C + b, sizeof(float) * (size_t)H);
+            for (int64_t h = 1; h < H; h <<= 1)
+                for (int64_t i = 0; i < H; i += 2 * h)
+                    for (int64_t j = i; j < i + h; ++j) {
+                        const float x0 = y[j], x1 = y[j + h];
+                        y[j] = x0 + x1;
+                        y[j + h] = x0 - x1;
+                    }
+            for (int64_t j = 0; j < H; ++j) y[j] *= norm;
+        }
+    return GI8O_OK;
+}
+
 int gi8o_quantize_blocks(const float *v, int8_t *q, float *scales, int64_t R, int64_t C, int64_t rb, int64_t cb)
 {
     if (R < 0 || C < 0 || rb <= 0 || cb <= 0) return GI8O_BAD_ARG;

@@ -58,10 +58,11 @@ def _load():
     lib.gi8o_matmul_scaled.argtypes = [p, p, p, p, p, i64, i64, i64]
     lib.gi8o_matmul_blockwise.argtypes = [p, p, p, i64, p, i64, p, p, i64, i64, i64]
     lib.gi8o_quantize_blocks.argtypes = [p, p, p, i64, i64, i64, i64]
+    lib.gi8o_hadamard_rotate.argtypes = [p, p, i64, i64, i64]
     lib.gi8o_set_num_threads.argtypes = [ctypes.c_int]
     lib.gi8o_num_threads.restype = ctypes.c_int
     for f in ("gi8o_matmul_i32", "gi8o_matmul", "gi8o_matmul_scaled", "gi8o_matmul_blockwise",
-              "gi8o_quantize_blocks"):
+              "gi8o_quantize_blocks", "gi8o_hadamard_rotate"):
         getattr(lib, f).restype = ctypes.c_int
     _lib = lib
     return lib
@@ -150,6 +151,15 @@ def c_quantize_blocks(v, rb, cb):
     s = np.empty((-(-R // rb), -(-C // cb)), np.float32)
     _check(_load().gi8o_quantize_blocks(_ptr(v), _ptr(q), _ptr(s), R, C, rb, cb), "quantize_blocks")
     return q, s
+
+
+def c_hadamard_rotate(v, block):
+    """Normalised Walsh-Hadamard rotation along the last axis in blocks of `block` (fp32, butterfly order)."""
+    v = _np(v, np.float32)
+    R, C = v.shape
+    out = np.empty((R, C), np.float32)
+    _check(_load().gi8o_hadamard_rotate(_ptr(v), _ptr(out), R, C, block), "hadamard_rotate")
+    return out
 
 
 # ------------------------------------------------------------------ numpy restatement

@@ -428,10 +428,53 @@ def test_quantiser_kernels_match_oracle(g, oracle, dtype):
         q, s = g.quantize_per_token(a.cuda())
         qr, sr = oracle.c_quantize_blocks(af, 1, K)
         assert np.array_equal(q.cpu().numpy(), qr) and np.array_equal(s.cpu().numpy(), sr.reshape(-1)), (dtype, M, K)
+    # Rounding boundaries and extreme scales: the kernels multiply by 1/s and fall back to the exact division near
+    # half-integers and for scales whose reciprocal is not accurate.
+    if dtype == torch.float32:
+        a = torch.zeros(6, 256)
+        a[0, 0] = 127.0                                   # scale exactly 1
+        a[0, 1:127] = torch.arange(1, 127) - 0.5          # exact ties: round half to even
+        a[1, 0] = 127.0
+        a[1, 1:127] = torch.nextafter(torch.arange(1, 127) - 0.5, torch.tensor(200.0))
+        a[2, 0] = 127.0
+        a[2, 1:127] = torch.nextafter(torch.arange(1, 127) - 0.5, torch.tensor(-200.0))
+        a[3, :128] = torch.randn(128, generator=gen) * 1e-38   # subnormal scale
+        a[4, :128] = torch.randn(128, generator=gen) * 1e35    # huge scale
+        a[5, :256] = torch.randn(256, generator=gen) * 3.3
+        a[:, 128:] = -a[:, :128] * 0.37
+        q, s = g.quantize_per_token_block(a.cuda())
+        qr, sr = oracle.c_quantize_blocks(a, 1, 128)
+        assert np.array_equal(q.cpu().numpy(), qr) and np.array_equal(s.cpu().numpy(), sr)
+        q, s = g.quantize_per_token(a.cuda())
+        qr, sr = oracle.c_quantize_blocks(a, 1, 256)
+        assert np.array_equal(q.cpu().numpy(), qr) and np.array_equal(s.cpu().numpy(), sr.reshape(-1))
     with pytest.raises(RuntimeError):
         g.quantize_per_token_block(torch.zeros(4, 130).cuda())       # K % 4 != 0
     with pytest.raises(RuntimeError):
         g.quantize_per_token_block(torch.zeros(4, 128))              # CPU tensor
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_hadamard_quantiser_matches_oracle(g, oracle, dtype):
+    """Fused Walsh-Hadamard rotation + per-token-per-128 quantiser: int8 values and scales equal the oracle's
+    rotate-then-quantise bit for bit, for every rotation block size the kernel has a code path for."""
+    gen = torch.Generator().manual_seed(111)
+    for (M, K, H) in [(3, 128, 128), (5, 768, 256), (2, 1536, 512), (4, 3072, 1024), (3, 2048, 2048), (2, 28672, 4096),
+                      (3, 8192, 8192), (2, 16384, 8192), (130, 8192, None)]:
+        a = (torch.randn(M, K, generator=gen) * 3).to(dtype)
+        a[:, 5] *= 20.0   # an outlier channel, which the rotation spreads over its block
+        a[0] = 0          # an all-zero row: scales 1, zeros
+        q, s = g.hadamard_quantize_per_token_block(a.cuda(), H)
+        block = H if H is not None else min(K & -K, 8192)
+        qr, sr = oracle.c_quantize_blocks(oracle.c_hadamard_rotate(a.float(), block), 1, 128)
+        assert np.array_equal(s.cpu().numpy(), sr), (dtype, M, K, H)
+        assert np.array_equal(q.cpu().numpy(), qr), (dtype, M, K, H)
+    with pytest.raises(RuntimeError):
+        g.hadamard_quantize_per_token_block(torch.zeros(4, 384).cuda(), 256)    # block does not divide K
+    with pytest.raises(RuntimeError):
+        g.hadamard_quantize_per_token_block(torch.zeros(4, 192).cuda(), 64)     # block below 128
+    with pytest.raises(RuntimeError):
+        g.hadamard_quantize_per_token_block(torch.zeros(4, 384).cuda(), 384)    # not a power of two
 
 
 def test_int8_linear_matches_oracle_pipeline(g, oracle):

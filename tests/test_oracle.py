@@ -145,3 +145,30 @@ def test_ulp_distance_helper(oracle):
     b = torch.tensor([1.0078125, -1.0078125, 0.0, 258.0]).bfloat16()
     d = oracle.bf16_ulp_distance(oracle.bf16_bits(a), oracle.bf16_bits(b))
     assert d.tolist() == [1, 1, 0, 1]
+
+
+def test_hadamard_rotation_oracle(oracle):
+    """The C rotation equals the package's torch restatement bit for bit, equals the Sylvester matrix product to
+    fp32 accuracy, is an involution up to rounding, and preserves the Euclidean norm."""
+    from scipy.linalg import hadamard
+
+    from gemm_int8_b200 import quant
+
+    gen = torch.Generator().manual_seed(5)
+    for (R, C, H) in [(3, 256, 128), (2, 1024, 1024), (2, 12288, 4096), (1, 8192, 8192)]:
+        a = torch.randn(R, C, generator=gen)
+        got = oracle.c_hadamard_rotate(a, H)
+        ref = quant.hadamard_rotate(a, H).numpy()
+        assert np.array_equal(got.view(np.uint32), ref.view(np.uint32)), (R, C, H)
+        back = oracle.c_hadamard_rotate(got, H)
+        assert np.abs(back - a.numpy()).max() < 1e-5
+        assert np.allclose(np.linalg.norm(got, axis=1), np.linalg.norm(a.numpy(), axis=1), rtol=1e-5)
+        if H <= 1024:
+            mat = hadamard(H).astype(np.float64) / np.sqrt(H)
+            exact = a.numpy().astype(np.float64).reshape(R, C // H, H) @ mat.T
+            assert np.abs(exact.reshape(R, C) - got).max() < 1e-5
+    one = np.zeros((1, 128), np.float32)
+    one[0, 0] = 1.0
+    assert np.array_equal(oracle.c_hadamard_rotate(one, 128), np.full((1, 128), np.float32(128 ** -0.5)))
+    with pytest.raises(Exception):
+        oracle.c_hadamard_rotate(np.zeros((1, 96), np.float32), 96)
