@@ -78,6 +78,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="skip the largest shapes")
     ap.add_argument("--out", default="")
+    ap.add_argument("--section", default="all", choices=["all", "gemm", "decode", "quant"],
+                    help="which part of the sweep to run")
     args = ap.parse_args()
     dev = torch.device("cuda")
     hbm, bf16, kind = _peaks()
@@ -100,6 +102,38 @@ def main():
 
     emit(f"Peaks: HBM {hbm} GB/s ({kind}), int8 tensor = 2 x bf16 {bf16} = {int8_peak:.0f} TOP/s ({kind}), nominal int8 {NOMINAL_INT8_TOPS:.0f} TOP/s")
     emit()
+    if args.section in ("all", "gemm"):
+        gemm_section(args, emit, tm, rnd, dev, int8_peak)
+    if args.section in ("all", "decode"):
+        decode_section(emit, tm, rnd, dev, hbm)
+    if args.section in ("all", "quant"):
+        quant_section(emit, tm, dev, hbm)
+    emit()
+    emit(f"kernel status word after the sweep: {g.device_status()}")
+    if args.out:
+        with open(args.out, "w") as f:
+            f.write("\n".join(lines) + "\n")
+
+
+def quant_section(emit, tm, dev, hbm):
+    """Activation quantisers: bytes = input + int8 output + scales, one cold-L2 launch per timed region."""
+    emit("Activation quantisers (per token per 128-wide K block), cold L2; bytes = input + int8 output + fp32 scales")
+    emit()
+    emit("| input | M | K | kernel | us | GB/s | of HBM peak |")
+    emit("|---|---|---|---|---|---|---|")
+    for dtype in (torch.bfloat16, torch.float32):
+        for (M, K) in ((2048, 4096), (2048, 8192), (16384, 8192), (8192, 28672)):
+            a = torch.randn(M, K, device=dev).to(dtype)
+            byt = M * K * (a.element_size() + 1) + M * (K // 128) * 4
+            for name, fn in (("quantize_token_block", lambda: g.quantize_per_token_block(a)),
+                             (f"hadamard_quantize_token_block (H = {min(K & -K, 8192)})",
+                              lambda: g.hadamard_quantize_per_token_block(a))):
+                t = tm.cold(fn)
+                emit(f"| {str(dtype).replace('torch.', '')} | {M} | {K} | {name} | {t * 1e3:.1f} | {byt / t / 1e6:.0f} | {byt / t / 1e6 / hbm:.3f} |")
+            del a
+
+
+def gemm_section(args, emit, tm, rnd, dev, int8_peak):
     emit("| config | M | N | K | kernel | ms | TOP/s | of 2x bf16 | of nominal | cuBLAS bf16 ms | speed-up vs bf16 | cuBLASLt int8 ms |")
     emit("|---|---|---|---|---|---|---|---|---|---|---|---|")
 
@@ -145,6 +179,9 @@ def main():
     if not args.quick:
         row("target", 16384, 16384, 16384, "plain", plain)
 
+
+
+def decode_section(emit, tm, rnd, dev, hbm):
     emit()
     emit("Decode shapes (config 3): per-token x per-channel scales, device time per kernel from CUDA-graph replays over HBM-cold weights")
     emit()
@@ -165,11 +202,6 @@ def main():
             emit(f"| {M} | {N} | {K} | {g.pick_variant(1, M, N, K)} | {t * 1e3:.1f} | {byt / t / 1e6:.0f} | {byt / t / 1e6 / hbm:.3f} | {tb * 1e3:.1f} | {tb / t:.2f}x |")
         del ys
 
-    emit()
-    emit(f"kernel status word after the sweep: {g.device_status()}")
-    if args.out:
-        with open(args.out, "w") as f:
-            f.write("\n".join(lines) + "\n")
 
 
 if __name__ == "__main__":
