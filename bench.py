@@ -373,7 +373,9 @@ def main():
     e2e = None
     if not args.no_e2e:
         host_in = [t.pin_memory() for t in inputs]
-        host_out = torch.empty((M, n_local), dtype=torch.bfloat16).pin_memory()
+        # N-shard: every rank reads back the gathered result ([world, M, N/world], the collective's block layout)
+        out_shape = (world, M, n_local) if (nshard and world > 1) else (M, n_local)
+        host_out = torch.empty(out_shape, dtype=torch.bfloat16).pin_memory()
         h2d = sum(t.numel() * t.element_size() for t in host_in)
         d2h = host_out.numel() * host_out.element_size()
         e2e_steps = max(3, min(args.steps, 20))
