@@ -506,6 +506,21 @@ def test_int8_linear_matches_oracle_pipeline(g, oracle):
     compiled = torch.compile(layer, dynamic=True)
     assert torch.equal(compiled(x.cuda()), y)
 
+    # Rotated layer: activations with outlier channels; bit-equal to the oracle pipeline, and closer to the fp32
+    # layer than the unrotated one.
+    xo = x.clone()
+    xo[..., 7] *= 40.0
+    xo[..., 300] *= 25.0
+    rot = g.Int8Linear.from_float(w, mode="blockwise", hadamard_block=1024).cuda()
+    yr = rot(xo.cuda())
+    xq, xs = oracle.c_quantize_blocks(oracle.c_hadamard_rotate(xo.reshape(-1, 1024), 1024), 1, 128)
+    wq, ws = oracle.c_quantize_blocks(oracle.c_hadamard_rotate(w, 1024), 128, 128)
+    assert np.array_equal(oracle.bf16_bits(yr.reshape(-1, 520)), oracle.c_matmul_blockwise(xq, wq, xs, ws))
+    dense_o = xo.reshape(-1, 1024) @ w.t()
+    err_rot = (yr.reshape(-1, 520).float().cpu() - dense_o).norm() / dense_o.norm()
+    err_plain = (layer(xo.cuda()).reshape(-1, 520).float().cpu() - dense_o).norm() / dense_o.norm()
+    assert err_rot < err_plain and err_rot < 0.02, (err_rot, err_plain)
+
 
 def test_host_pipeline_matches_oracle(g, oracle):
     """Host-buffer front end: pinned operands in, pinned result out, several calls in flight; every result is
