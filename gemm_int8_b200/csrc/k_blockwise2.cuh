@@ -18,54 +18,6 @@
 
 namespace gi8 {
 
-GI8_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar_cluster_addr, int32_t c0,
-                                 int32_t c1)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.cta_group::2"
-        " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(smem_dst)),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(leader_bar_cluster_addr), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-GI8_DEVICE void umma_i8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
-        "}\n" ::"r"(tmem_d),
-        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// One arrival on the barrier at cluster address `bar_cluster_addr` once all MMAs issued so far have completed.
-GI8_DEVICE void umma_commit_pair(uint32_t bar_cluster_addr)
-{
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster_addr)
-                 : "memory");
-}
-
-GI8_DEVICE void mbar_arrive_cluster(uint32_t bar_cluster_addr)
-{
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
-}
-
-GI8_DEVICE void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols)
-{
-    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
-                 "r"(ncols)
-                 : "memory");
-}
-
-GI8_DEVICE void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
-
-GI8_DEVICE void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols)
-{
-    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-
 constexpr int kPairBM = 256;  // rows of the pair's tile (128 per CTA)
 
 #ifdef GI8_ENABLE_ABLATIONS

@@ -247,34 +247,6 @@ smallm_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 // scales and stores bf16.  No global scratch, no atomics, and the sum is exact whatever the order.
 // The two cluster barriers are hardware barriers that every thread of every CTA reaches unconditionally.
 // ---------------------------------------------------------------------------------------------------
-GI8_DEVICE void cluster_sync_all()
-{
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-GI8_DEVICE uint32_t cluster_cta_rank()
-{
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-
-// Address of `local_smem_addr` in the shared memory of cluster CTA `rank`.
-GI8_DEVICE uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank)
-{
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_smem_addr), "r"(rank));
-    return r;
-}
-
-GI8_DEVICE int32_t ld_dsmem_s32(uint32_t cluster_addr)
-{
-    int32_t v;
-    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
-    return v;
-}
-
 template <int MT, int STAGES>
 __global__ void __launch_bounds__(kSmallMThreads)
 smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
