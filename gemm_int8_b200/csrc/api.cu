@@ -220,9 +220,50 @@ int launch_dense(DeviceState* st, int slot, const int8_t* x, const int8_t* y, De
     return GI8_OK;
 }
 
+// Two-CTA form of the dense kernel: 256 x 256 tiles, one CTA pair (2 x 1 x 1 cluster) per tile.
+template <int EPI>
+int launch_dense_pair(DeviceState* st, int slot, const int8_t* x, const int8_t* y, DenseParams p, cudaStream_t stream)
+{
+    constexpr int BN = 256, STAGES = 6;
+    constexpr size_t kStoreStage = 4 * 2 * 2048;
+    constexpr size_t smem = static_cast<size_t>(STAGES) * (kBM + BN / 2) * kBK + kStoreStage + 1024;
+    auto kernel = dense_gemm_kernel<BN, STAGES, EPI, true>;
+    if (int rc = ensure_smem(st, slot, kernel, smem)) return rc;
+    CUtensorMap mx, my, mo;
+    if (int rc = make_operand_map(&mx, x, p.M, p.K, kBM)) return rc;
+    if (int rc = make_operand_map(&my, y, p.N, p.K, BN / 2)) return rc;
+    const char* ts = getenv("GEMM_INT8_TMA_STORE");
+    p.tma_store = (EPI != EPI_RAW_I32) && p.vec_ok && !(ts && ts[0] == '0');
+    if (p.tma_store) {
+        if (int rc = make_output_map(&mo, p.out, p.M, p.N, p.ldo)) return rc;
+    } else {
+        mo = mx;  // unused by the kernel
+    }
+    p.tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
+    p.tiles_n = (p.N + BN - 1) / BN;
+    p.group_m = pick_group_m(p.K) / 2 > 0 ? pick_group_m(p.K) / 2 : 1;
+    const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+    const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(kDenseThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mx, my, mo, p));
+    return GI8_OK;
+}
+
 template <int EPI>
 int dispatch_dense(DeviceState* st, const int8_t* x, const int8_t* y, DenseParams p, cudaStream_t stream)
 {
+    if (g_forced_variant == VAR_PAIR) return launch_dense_pair<EPI>(st, 45 + EPI, x, y, p, stream);
     int bn;
     switch (g_forced_variant) {
         case VAR_DENSE_BN256: bn = 256; break;

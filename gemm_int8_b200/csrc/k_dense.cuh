@@ -92,18 +92,26 @@ GI8_DEVICE void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb
     nb = r / rows;
 }
 
-template <int BN, int STAGES, int EPI>
+// PAIR: two CTAs on neighbouring SMs (a 2 x 1 x 1 cluster) share one 256 x BN tile.  The leader's MMA thread issues
+// tcgen05.mma.cta_group::2 (M = 256), which reads each CTA's own 128 rows of x and each CTA's half of the BN rows
+// of y from that CTA's shared memory, so a CTA loads (128 + BN/2) x 128 bytes per K block instead of (128 + BN) x 128
+// -- a third less L2 traffic per MAC at BN = 256 -- and each CTA keeps the accumulators of its 128 rows in its own
+// tensor memory.  Every TMA load is unicast into the issuing CTA's shared memory and signals the leader's barrier;
+// the MMA thread commits to each CTA's barrier with its own unicast tcgen05.commit (no multicast anywhere).
+template <int BN, int STAGES, int EPI, bool PAIR = false>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                   const __grid_constant__ CUtensorMap map_out, const DenseParams p)
 {
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN must be a multiple of 32 up to 256");
     constexpr uint32_t kBytesA = kBM * kBK;
-    constexpr uint32_t kBytesB = BN * kBK;
+    constexpr int kTileM = PAIR ? 2 * kBM : kBM;       // rows of the (pair's) tile
+    constexpr int kRowsB = PAIR ? BN / 2 : BN;         // rows of y this CTA loads
+    constexpr uint32_t kBytesB = kRowsB * kBK;
     constexpr uint32_t kStageBytes = kBytesA + kBytesB;
     constexpr uint32_t kTmemCols = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
                                  : (2 * BN <= 256) ? 256 : 512;
-    constexpr uint32_t kIdesc = make_idesc_i8(kBM, BN, false);
+    constexpr uint32_t kIdesc = make_idesc_i8(kTileM, BN, false);
 
     extern __shared__ uint8_t smem_raw[];
     // 128B-swizzled tiles need 1024-byte alignment.
@@ -120,8 +128,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_tiles = p.tiles_m * p.tiles_n;   // tiles_m counts kTileM-row tiles
     const int num_kb = (p.K + kBK - 1) / kBK;
+    // PAIR: rank 0 is the leader (its bar_full and bar_acc_empty serve both CTAs); the pair is the scheduling unit.
+    const uint32_t rank = PAIR ? cluster_cta_rank() : 0u;
+    const int first_tile = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -131,7 +143,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(&bar_acc_full[b], 1);
-            mbar_init(&bar_acc_empty[b], 4);
+            mbar_init(&bar_acc_empty[b], PAIR ? 8 : 4);
         }
         fence_barrier_init();
         prefetch_tensormap(&map_x);
@@ -139,11 +151,17 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (p.tma_store) prefetch_tensormap(&map_out);
     }
     if (warp == 1) {
-        tmem_alloc(&tmem_base_slot, kTmemCols);
-        tmem_relinquish_alloc_permit();
+        if constexpr (PAIR) {
+            tmem_alloc_pair(&tmem_base_slot, kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(&tmem_base_slot, kTmemCols);
+            tmem_relinquish_alloc_permit();
+        }
     }
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers exist before anything signals them remotely
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
@@ -152,7 +170,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (lane == 0) {
             uint32_t it = 0;  // running stage counter across tiles
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
                 int mb, nb;
                 tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
@@ -165,13 +183,22 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     }
                     uint8_t* sa = smem + s * kStageBytes;
                     uint8_t* sb = sa + kBytesA;
-                    mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
-                    tma_load_2d(sa, &map_x, &bar_full[s], kb * kBK, mb * kBM);
-                    tma_load_2d(sb, &map_y, &bar_full[s], kb * kBK, nb * BN);
+                    if constexpr (PAIR) {
+                        // The leader arms its barrier for the bytes of BOTH CTAs; the peer only sends bytes.
+                        const uint32_t leader_full = map_to_cta(smem_u32(&bar_full[s]), 0);
+                        if (rank == 0) mbar_arrive_expect_tx(&bar_full[s], 2 * kStageBytes);
+                        tma_load_2d_pair(sa, &map_x, leader_full, kb * kBK, mb * kTileM + static_cast<int>(rank) * kBM);
+                        tma_load_2d_pair(sb, &map_y, leader_full, kb * kBK, nb * BN + static_cast<int>(rank) * kRowsB);
+                    } else {
+                        mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
+                        tma_load_2d(sa, &map_x, &bar_full[s], kb * kBK, mb * kBM);
+                        tma_load_2d(sb, &map_y, &bar_full[s], kb * kBK, nb * BN);
+                    }
                 }
             }
-            // Drain: every armed stage must have landed before the CTA may exit.
-            const uint32_t armed = it < STAGES ? it : STAGES;
+            // Drain: every armed stage must have landed before the CTA may exit (PAIR: the leader's barriers
+            // complete only when both CTAs' bytes have landed; the peer leaves through the final cluster barrier).
+            const uint32_t armed = (PAIR && rank != 0) ? 0u : (it < STAGES ? it : STAGES);
             for (uint32_t j = 0; j < armed; ++j) {
                 const uint32_t i2 = it - 1 - j;
                 if (!mbar_wait(&bar_full[i2 % STAGES], (i2 / STAGES) & 1)) {
@@ -182,11 +209,11 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {
             uint32_t it = 0;
             uint32_t local_tile = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
                 const uint32_t buf = local_tile & 1;
                 const uint32_t acc_ph = (local_tile >> 1) & 1;
                 if (!wait_or_abort(&bar_acc_empty[buf], acc_ph ^ 1, &abort_flag)) {
@@ -210,11 +237,25 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 #pragma unroll
                     for (int k = 0; k < kBK / kUmmaK; ++k) {
                         // +2 in the start-address field = +32 bytes = one UMMA K step inside the swizzled row
-                        umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0);
+                        if constexpr (PAIR) umma_i8_pair(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0);
+                        else umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0);
                     }
-                    umma_commit(&bar_empty[s]);  // frees the stage once these MMAs have read it
+                    // frees the stage (in both CTAs) once these MMAs have read it
+                    if constexpr (PAIR) {
+                        umma_commit_pair(map_to_cta(smem_u32(&bar_empty[s]), 0));
+                        umma_commit_pair(map_to_cta(smem_u32(&bar_empty[s]), 1));
+                    } else {
+                        umma_commit(&bar_empty[s]);
+                    }
                 }
-                if (ok) umma_commit(&bar_acc_full[buf]);
+                if (ok) {
+                    if constexpr (PAIR) {
+                        umma_commit_pair(map_to_cta(smem_u32(&bar_acc_full[buf]), 0));
+                        umma_commit_pair(map_to_cta(smem_u32(&bar_acc_full[buf]), 1));
+                    } else {
+                        umma_commit(&bar_acc_full[buf]);
+                    }
+                }
             }
         }
     } else {
@@ -222,7 +263,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
         uint32_t local_tile = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++local_tile) {
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
             int mb, nb;
             tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
             const uint32_t buf = local_tile & 1;
@@ -233,7 +274,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                 break;
             }
             tcgen05_fence_after_sync();
-            const int row = mb * kBM + quarter * 32 + lane;
+            const int row = mb * kTileM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
             float row_scale = 1.0f;
@@ -275,7 +316,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                         // 32 rows x 32 bf16 of this warp go to shared memory in the 64-byte-swizzled layout the
                         // output tensor map expects (16-byte chunk index xor (row / 2) % 4: conflict-free), then one
                         // lane issues the TMA store; rows and columns beyond M and N are clipped by the hardware.
-                        const int row0 = mb * kBM + quarter * 32;
+                        const int row0 = mb * kTileM + static_cast<int>(rank) * kBM + quarter * 32;
                         if (row0 < p.M) {
                             uint8_t* stg = store_stage + ((warp - 2) * 2 + ((c >> 5) & 1)) * 2048;
                             if (lane == 0) tma_store_wait_read<1>();  // the block staged two chunks ago has been read
@@ -314,7 +355,10 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
             // All of this warp's reads of the accumulator buffer are complete: hand it back.
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bar_acc_empty[buf]);
+            if (lane == 0) {
+                if constexpr (PAIR) mbar_arrive_cluster(map_to_cta(smem_u32(&bar_acc_empty[buf]), 0));
+                else mbar_arrive(&bar_acc_empty[buf]);
+            }
         }
         // Outstanding TMA stores read this CTA's shared memory: they must have completed before it exits.
         if (lane == 0) tma_store_wait_all<0>();
@@ -322,10 +366,12 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // neither CTA leaves while the other may still read or signal it
     if (warp == 1) {
         __syncwarp();
         tcgen05_fence_after_sync();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+        else tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 

@@ -15,7 +15,7 @@ import torch
 pytestmark = pytest.mark.gpu
 
 GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
-DENSE_VARIANTS = ["dense_bn64", "dense_bn128", "dense_bn256"]
+DENSE_VARIANTS = ["dense_bn64", "dense_bn128", "dense_bn256", "pair"]
 
 
 @pytest.fixture(scope="module")
