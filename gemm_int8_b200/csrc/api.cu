@@ -14,6 +14,7 @@
 #include "k_blockwise.cuh"
 #include "k_blockwise2.cuh"
 #include "k_dense.cuh"
+#include "k_gemv.cuh"
 #include "k_quant.cuh"
 #include "k_smallm.cuh"
 
@@ -44,16 +45,16 @@ int fail(int code, const char* fmt, ...)
 // Kernel status word: one instance per device (module-scope device variable).
 __device__ uint32_t g_kernel_status;
 
-enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM, VAR_SMALLM_CLUSTER, VAR_PAIR };
-const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "smallm_cluster", "pair"};
-constexpr int kNumVariants = 7;
+enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM, VAR_SMALLM_CLUSTER, VAR_PAIR, VAR_GEMV };
+const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "smallm_cluster", "pair", "gemv"};
+constexpr int kNumVariants = 8;
 int g_forced_variant = VAR_AUTO;
 
 struct DeviceState {
     bool ready = false;
     int sm_count = 0;
     uint32_t* status = nullptr;
-    bool attr_set[48] = {};
+    bool attr_set[64] = {};
 };
 
 std::mutex g_mutex;
@@ -292,6 +293,65 @@ int zero_output(void* out, int64_t bytes, cudaStream_t stream)
 }
 
 // ---------------------------------------------------------------------------------------------------
+// Fewest tokens: the weight-streaming dp4a kernel (no tensor memory, no TMA, no set-up).  Measured against the
+// cluster split-K kernel on B200 (CUDA-graph replays over HBM-cold weights) it is 0.3-0.5 us faster at M = 1,
+// K = 4096 and slower everywhere else (M = 4: 6.9 vs 6.7 us at 4096 x 4096, 17.2 vs 13.6 us at K = 14336), so the
+// fixed cost of the decode shapes is launch and ramp-up, not the tensor-core set-up.  Kept as the selectable
+// variant "gemv"; the automatic dispatch does not use it unless GEMM_INT8_GEMV_M raises the limit.
+// ---------------------------------------------------------------------------------------------------
+constexpr int kGemvMaxM = 8;     // the kernel exists for token tiles 1, 2, 4, 8
+int g_gemv_auto_m = 0;           // the automatic dispatch uses it up to this M (GEMM_INT8_GEMV_M overrides)
+constexpr int64_t kGemvMaxSmem = 200 * 1024;
+
+template <int MT>
+int launch_gemv(DeviceState* st, int slot, const GemvParams& p, cudaStream_t stream)
+{
+    const size_t smem = static_cast<size_t>(MT) * p.K;
+    auto kernel = gemv_scaled_kernel<MT>;
+    // the opt-in limit is set once per kernel, so to the largest size any K may need
+    if (int rc = ensure_smem(st, slot, kernel, static_cast<size_t>(kGemvMaxSmem))) return rc;
+    const int warps_per_cta = kGemvThreads / 32;
+    int grid = (p.N + warps_per_cta - 1) / warps_per_cta;
+    const int cap = st->sm_count * 8;
+    if (grid > cap) grid = cap;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid, 1, 1);
+    cfg.blockDim = dim3(kGemvThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    const char* pdl = getenv("GEMM_INT8_PDL");
+    cfg.numAttrs = (pdl && pdl[0] == '0') ? 0 : 1;
+    GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
+    return GI8_OK;
+}
+
+bool gemv_applies(int64_t M, int64_t K, bool forced)
+{
+    int limit = g_gemv_auto_m;
+    if (const char* e = getenv("GEMM_INT8_GEMV_M")) limit = atoi(e);
+    if (forced) limit = kGemvMaxM;
+    if (M < 1 || M > limit || M > kGemvMaxM) return false;
+    const int mt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
+    return static_cast<int64_t>(mt) * K <= kGemvMaxSmem;
+}
+
+int dispatch_gemv(DeviceState* st, const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out,
+                  int64_t M, int64_t N, int64_t K, cudaStream_t stream)
+{
+    GemvParams p{};
+    p.x = x, p.w = y, p.sx = sx, p.sw = sw, p.out = static_cast<uint16_t*>(out), p.ldo = N;
+    p.M = (int)M, p.N = (int)N, p.K = (int)K;
+    if (M <= 1) return launch_gemv<1>(st, 48, p, stream);
+    if (M <= 2) return launch_gemv<2>(st, 49, p, stream);
+    if (M <= 4) return launch_gemv<4>(st, 50, p, stream);
+    return launch_gemv<8>(st, 51, p, stream);
+}
+
+// ---------------------------------------------------------------------------------------------------
 // Small-M plan: token tile MT, number of K splits and pipeline depth.  Fitted on B200 with device-timed CUDA-graph
 // replays over HBM-cold weights (M in {1,16,64} x {4096x4096, 14336x4096, 4096x14336}): few weight tiles want the
 // largest cluster (8 splits: 32 tiles -> 256 CTAs), many weight tiles want one or two; for M >= 16 the reduction
@@ -477,6 +537,7 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
     int dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
     if (g_forced_variant != VAR_AUTO) return kVariantNames[g_forced_variant];
+    if (kind == 1 && gemv_applies(M, K, false)) return "gemv";
     if (kind == 1 && plan_smallm(M, N, K, sms, false).use) return "smallm_cluster";
     const int bn = pick_bn(M, N, sms, kind == 2);
     return bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
@@ -543,6 +604,8 @@ int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const f
     if (int rc = get_device_state(&st)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (K == 0) return zero_output(out, M * N * 2, s);
+    if ((g_forced_variant == VAR_AUTO || g_forced_variant == VAR_GEMV) && gemv_applies(M, K, g_forced_variant == VAR_GEMV))
+        return dispatch_gemv(st, x, y, sx, sw, out, M, N, K, s);
     if (g_forced_variant == VAR_AUTO || g_forced_variant == VAR_SMALLM_CLUSTER) {
         const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, g_forced_variant == VAR_SMALLM_CLUSTER, kMaxClusterSplits);
         if (pl.use) {

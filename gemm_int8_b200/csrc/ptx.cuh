@@ -372,6 +372,16 @@ GI8_DEVICE uint32_t pack_bf16x2(float lo, float hi)
     return r;
 }
 
+// 16-byte streaming load: read-only path, no L1 allocation (the data is used once).
+GI8_DEVICE uint4 ld_nc_na(const uint4* p)
+{
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
 GI8_DEVICE uint16_t to_bf16_bits(float f)
 {
     uint16_t r;

@@ -137,7 +137,8 @@ int gi8_hadamard_quantize_token_block(const void* in, int in_dtype, int8_t* q, f
  * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted
  * per-shape dispatch that replaces the reference's shape table (csrc/kernels/gemm.cu:136-161).
  * Names: "dense_bn256", "dense_bn128", "dense_bn64", "smallm" (split-K through global scratch),
- * "smallm_cluster" (split-K through distributed shared memory), "pair" (two-CTA tiles with
+ * "smallm_cluster" (split-K through distributed shared memory), "gemv" (weight-streaming dp4a kernel for
+ * M <= 8 of the scaled entry point), "pair" (two-CTA tiles with
  * tcgen05.mma.cta_group::2: 256 x 256 for the dense entry points, 256 x 128 for the blockwise one), "auto".  Returns GI8_ERR_INVALID_ARGUMENT
  * for an unknown name.
  */

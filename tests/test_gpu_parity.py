@@ -158,7 +158,7 @@ def test_reference_benchmark_shapes(g, oracle):
 
 
 # ---------------------------------------------------------------------------------------- scaled (per token x per channel)
-@pytest.mark.parametrize("variant", DENSE_VARIANTS + ["smallm", "smallm_cluster", None])
+@pytest.mark.parametrize("variant", DENSE_VARIANTS + ["smallm", "smallm_cluster", "gemv", None])
 def test_scaled_edge_shapes(g, oracle, variant):
     g.force_variant(variant)
     gen = torch.Generator().manual_seed(41)
@@ -178,9 +178,10 @@ def test_config3_decode_shapes(g, oracle, K, N):
 
     for M in (1, 4, 16, 64):
         xq, wq, sx, sw = workloads.decode(M, N, K)
-        assert g.pick_variant(1, M, N, K) == "smallm_cluster"
+        assert g.pick_variant(1, M, N, K) in ("smallm_cluster", "gemv")
         ref = oracle.c_matmul_scaled(xq, wq, sx, sw)
-        for variant in (None, "smallm"):     # cluster reduction (default) and global-scratch reduction
+        # the automatic choice, the cluster reduction, the global-scratch reduction and the streaming kernel
+        for variant in (None, "smallm_cluster", "smallm", "gemv"):
             g.force_variant(variant)
             out = g.matmul_scaled(xq.cuda(), wq.cuda(), sx.cuda(), sw.cuda())
             assert_bits_equal(oracle, out, ref, f"decode {variant} M={M} N={N} K={K}")
