@@ -9,7 +9,7 @@
 //   * dp4a (four int8 MACs into int32, exact) -- 4*M per 16 weight bytes and lane, far below the integer rate at
 //     the byte rate HBM delivers;
 //   * warp shuffle reduction, then the same epilogue arithmetic as the other kernels (scales multiplied first).
-// Integer sums are exact in any order, so the result is bit-identical to the tensor-core kernels and the oracle.
+// Integer sums are exact in any order, so the result is bit-identical to that of the tensor-core kernels.
 #pragma once
 
 #include "ptx.cuh"
