@@ -1,8 +1,10 @@
 // Weight-streaming kernel for the fewest tokens (M <= 8) of the per-token x per-channel entry point:
 //   out[m,n] = bf16( fp32( sum_k x[m,k] * w[n,k] ) * (sx[m] * sw[n]) )
-// At these sizes the work is reading N*K weight bytes once; arithmetic intensity is M MACs per byte.  The
-// tensor-core kernels pay a fixed 4-5 us (tensor-memory allocation, barrier set-up, first TMA round trip, cluster
-// reduction) that is as long as the whole stream of a 17 MB weight; this kernel has no set-up at all:
+// At these sizes the work is reading N*K weight bytes once; arithmetic intensity is M MACs per byte.  This kernel
+// does that without tensor memory, TMA, barriers or a cluster reduction, to find out whether the fixed 3-4 us the
+// tensor-core small-M kernels spend above their HBM time is their set-up.  It is not: measured on B200 this kernel
+// needs the same fixed time (6.0 vs 6.5 us at M = 1 on a 17 MB weight, slower from M = 2 on), so it is a selectable
+// variant ("gemv") and not part of the automatic dispatch.
 //   * one warp per output channel n: the K bytes of w[n,:] are read with 16-byte loads, 512 contiguous bytes per
 //     warp and load, kGemvUnroll loads in flight per lane;
 //   * the tokens (M*K bytes) sit in shared memory, read with 16-byte loads at the same k;
