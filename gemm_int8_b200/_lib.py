@@ -33,6 +33,12 @@ SYMBOLS = {
     "gi8_matmul_scaled_workspace_bytes": (_i64, [_i64, _i64, _i64]),
     "gi8_matmul_scaled_static": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "gi8_matmul_blockwise": (_i, [_p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p]),
+    "gi8_matmul_blockwise_allgather": (_i, [_p, _p, _p, _i64, _p, _i64, _p, _i, _i64, _i64, _i64, _i64, _i64, _p]),
+    "gi8_peer_alloc": (_i, [_p, _i64]),
+    "gi8_peer_free": (_i, [_p]),
+    "gi8_peer_export": (_i, [_p, _p]),
+    "gi8_peer_import": (_i, [_p, _p]),
+    "gi8_peer_release": (_i, [_p]),
     "gi8_quantize_token_block": (_i, [_p, _i, _p, _p, _i64, _i64, _p]),
     "gi8_quantize_token": (_i, [_p, _i, _p, _p, _i64, _i64, _p]),
     "gi8_hadamard_quantize_token_block": (_i, [_p, _i, _p, _p, _i64, _i64, _i64, _p]),

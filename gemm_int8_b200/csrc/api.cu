@@ -770,9 +770,14 @@ int gi8_quantize_token(const void* in, int in_dtype, int8_t* q, float* scales, i
     return GI8_OK;
 }
 
-int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
-                         int64_t ld_sw, void* out, int64_t M, int64_t N, int64_t K, void* stream)
+// gather != nullptr: the N-sharded form.  This GEMM's [M,N] result is columns [col0, col0 + N) of an [M, n_total]
+// matrix, and the epilogue writes every block into all n_out such matrices (gather[i]: this rank's own and every
+// peer's, the latter through mapped peer memory) instead of `out`.
+static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw, int64_t ld_sw,
+                          void* out, int64_t M, int64_t N, int64_t K, void* stream, void* const* gather, int n_out,
+                          int64_t n_total, int64_t col0)
 {
+    if (gather) out = gather[0];
     if (int rc = check_common(x, y, out, M, N, K, 2)) return rc;
     if (M == 0 || N == 0) return GI8_OK;
     DeviceState* st;
@@ -793,9 +798,10 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
     p.out = out, p.sa = sa, p.sw = sw, p.status = st->status, p.ldo = N, p.ld_sa = ld_sa, p.ld_sw = ld_sw;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
+    p.n_out = 1, p.out_col0 = 0;
     CUtensorMap mx, my;
     if (int rc = make_operand_map(&mx, x, M, K, kBM)) return rc;
-    if (g_forced_variant == VAR_PAIR) {
+    if (g_forced_variant == VAR_PAIR && !gather) {
         // Two-CTA form: 256 x 128 tiles, one CTA pair per tile.
         if (int rc = make_operand_map(&my, y, N, K, 64)) return rc;
         p.tiles_m = (int)((M + kPairBM - 1) / kPairBM);
@@ -828,20 +834,22 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
         case VAR_DENSE_BN64: bn = 64; break;
         default: bn = pick_bn(M, N, st->sm_count, true);
     }
+    if (gather && bn == 64) bn = 128;  // the narrow tile has no TMA-store epilogue
     p.tiles_m = (int)((M + kBM - 1) / kBM);
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.group_m = pick_group_m(p.K);
     const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
-    CUtensorMap mo;
-    {
+    OutputMaps mo{};
+    if (gather) {
+        for (int i = 0; i < n_out; ++i)
+            if (int rc = make_output_map(&mo.m[i], gather[i], M, n_total, n_total)) return rc;
+        p.tma_store = 1, p.n_out = n_out, p.out_col0 = static_cast<int>(col0);
+    } else {
         const char* ts = getenv("GEMM_INT8_TMA_STORE");
         p.tma_store = p.vec_ok && !(ts && ts[0] == '0');
-        if (p.tma_store) {
-            if (int rc = make_output_map(&mo, out, M, N, N)) return rc;
-        } else {
-            mo = mx;  // unused by the kernel
-        }
+        if (p.tma_store)
+            if (int rc = make_output_map(&mo.m[0], out, M, N, N)) return rc;
     }
     // Tuning knobs (not part of the ABI; every combination gives bit-identical results):
     //   GEMM_INT8_PROMOTION = 0 | 1 | 2 | 9   promotion arithmetic (default 9, the biased accumulator; 3..8 are
@@ -901,6 +909,67 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
 #undef GI8_LAUNCH_BW
 #undef GI8_LAUNCH_BWP
     GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
+}
+
+int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                         int64_t ld_sw, void* out, int64_t M, int64_t N, int64_t K, void* stream)
+{
+    return blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, out, M, N, K, stream, nullptr, 1, N, 0);
+}
+
+int gi8_matmul_blockwise_allgather(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                                   int64_t ld_sw, void* const* outs, int n_outs, int64_t M, int64_t N, int64_t K,
+                                   int64_t n_total, int64_t col0, void* stream)
+{
+    if (!outs || n_outs < 1 || n_outs > kMaxOutputs)
+        return fail(GI8_ERR_INVALID_ARGUMENT, "n_outs must be in [1, %d]", kMaxOutputs);
+    for (int i = 0; i < n_outs; ++i)
+        if (!outs[i] || reinterpret_cast<uintptr_t>(outs[i]) % 16)
+            return fail(GI8_ERR_MISALIGNED, "output %d is null or not 16-byte aligned", i);
+    if (col0 < 0 || N < 0 || col0 + N > n_total || n_total % 8 || col0 % 32 || (N % 32 && col0 + N != n_total))
+        return fail(GI8_ERR_UNSUPPORTED_SHAPE, "column slice [%lld, %lld) of %lld: n_total must be a multiple of 8, the "
+                    "slice must start at a multiple of 32 and end at one (or at n_total)", (long long)col0,
+                    (long long)(col0 + N), (long long)n_total);
+    if (M > 0 && N > 0 && K == 0) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "K must be positive for the gathering form");
+    return blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, nullptr, M, N, K, stream, outs, n_outs, n_total, col0);
+}
+
+// Peer buffers for the gathering form: plain cudaMalloc allocations (an IPC handle names a whole allocation) and the
+// CUDA IPC calls, so that a host without its own peer-memory plumbing can map every rank's output matrix.
+int gi8_peer_alloc(void** ptr, int64_t bytes)
+{
+    if (!ptr || bytes <= 0) return fail(GI8_ERR_INVALID_ARGUMENT, "bad peer allocation request");
+    GI8_CUDA(cudaMalloc(ptr, static_cast<size_t>(bytes)));
+    return GI8_OK;
+}
+
+int gi8_peer_free(void* ptr)
+{
+    GI8_CUDA(cudaFree(ptr));
+    return GI8_OK;
+}
+
+int gi8_peer_export(void* ptr, void* handle64)
+{
+    if (!ptr || !handle64) return fail(GI8_ERR_INVALID_ARGUMENT, "null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles are 64 bytes");
+    GI8_CUDA(cudaIpcGetMemHandle(static_cast<cudaIpcMemHandle_t*>(handle64), ptr));
+    return GI8_OK;
+}
+
+int gi8_peer_import(const void* handle64, void** ptr)
+{
+    if (!ptr || !handle64) return fail(GI8_ERR_INVALID_ARGUMENT, "null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    GI8_CUDA(cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess));
+    return GI8_OK;
+}
+
+int gi8_peer_release(void* ptr)
+{
+    GI8_CUDA(cudaIpcCloseMemHandle(ptr));
     return GI8_OK;
 }
 

@@ -70,6 +70,14 @@ struct BlockwiseParams {
     int vec_ok;  // out is 16-byte aligned and ldo % 8 == 0
     int group_m; // row-blocks per rasterisation band
     int tma_store;  // stage 32 x 32 bf16 blocks in shared memory and write them with TMA stores
+    int n_out;      // number of output matrices the TMA-store epilogue writes every block to (1, or the ranks of an
+                    // N-sharded group: each rank's full [M, N_total] matrix, peers through mapped peer memory)
+    int out_col0;   // column of this GEMM's first output column in those matrices
+};
+
+constexpr int kMaxOutputs = 8;
+struct OutputMaps {
+    CUtensorMap m[kMaxOutputs];
 };
 
 GI8_DEVICE uint64_t pack_f32x2(uint32_t lo_bits, uint32_t hi_bits)
@@ -154,7 +162,7 @@ enum PartialPipe : int { PIPE_X16_DOUBLE = 0, PIPE_X32_DOUBLE = 1, PIPE_X32_SING
 template <int BN, int STAGES, int PROMO, int PIPE = PIPE_X16_DOUBLE, int SPLIT = 1>
 __global__ void __launch_bounds__(kBlockwiseThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
-                      const __grid_constant__ CUtensorMap map_out, const BlockwiseParams p)
+                      const __grid_constant__ OutputMaps outs, const BlockwiseParams p)
 {
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
     static_assert(SPLIT == 1 || (SPLIT == 2 && BN == 256), "column halves only for the 256-wide tile");
@@ -602,10 +610,13 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                             fence_proxy_async_smem();
                             __syncwarp();
                             if (lane == 0) {
-                                asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
-                                                 reinterpret_cast<uint64_t>(&map_out)),
-                                             "r"(stg), "r"(col_base + c), "r"(row0)
-                                             : "memory");
+                                // one store per output matrix (the local one, and in an N-sharded group every
+                                // peer's, through its mapped memory: plain unicast TMA stores)
+                                for (int o = 0; o < p.n_out; ++o)
+                                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                                     reinterpret_cast<uint64_t>(&outs.m[o])),
+                                                 "r"(stg), "r"(p.out_col0 + col_base + c), "r"(row0)
+                                                 : "memory");
                                 tma_store_commit();
                             }
                         }

@@ -100,3 +100,108 @@ def matmul_blockwise_nsharded(x_q: torch.Tensor, w_q_shard: torch.Tensor, x_scal
         blocks = all_gather_slices(local, group=group)
         return assemble_row_major(blocks) if row_major else blocks
     return all_gather_ragged(local, N, group=group)
+
+
+class FusedGatherGemm:
+    """N-sharded blockwise GEMM whose epilogue writes every output block straight into every rank's full
+    [M, N] matrix (TMA stores through mapped peer memory), so the all-gather rides on the GEMM tile by tile and no
+    collective or permuting copy follows.
+
+    Set-up (once per output shape): every rank allocates its [M, N] bf16 matrix with the library's peer allocator,
+    the CUDA IPC handles are exchanged through `torch.distributed` (object all-gather: host side, any backend), and
+    each rank maps the others' matrices.  Per call: one kernel launch, then a barrier (`torch.distributed.barrier`
+    on the same stream) after which `result()` is complete on every rank.  Ranks must be processes on one node with
+    peer access between their GPUs; no multicast is used.
+    """
+
+    def __init__(self, M: int, N: int, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+
+        from . import _C, _lib
+
+        self._C, self._lib, self._ct = _C, _lib, ctypes
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("FusedGatherGemm supports at most 8 ranks")
+        self.M, self.N = M, N
+        self.lo, self.hi = shard_bounds(N, self.world, self.rank)
+        if N % 8 or self.lo % 32 or (self.hi % 32 and self.hi != N):
+            raise ValueError("N must be a multiple of 8 and every shard a multiple of 32 columns")
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        nbytes = M * N * 2
+        own = ctypes.c_void_p()
+        _lib.check(_C, _C.gi8_peer_alloc(ctypes.byref(own), nbytes))
+        self._own = own
+        handle = (ctypes.c_ubyte * 64)()
+        _lib.check(_C, _C.gi8_peer_export(own, handle))
+        handles = [None] * self.world
+        dist.all_gather_object(handles, bytes(handle), group=group)
+        self._mapped = []
+        ptrs = []
+        for r, h in enumerate(handles):
+            if r == self.rank:
+                ptrs.append(own.value)
+                continue
+            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+            p = ctypes.c_void_p()
+            _lib.check(_C, _C.gi8_peer_import(buf, ctypes.byref(p)))
+            self._mapped.append(p)
+            ptrs.append(p.value)
+        # own matrix first (the entry point takes any order; outs[0] is only used for argument checks)
+        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+        self._outs = (ctypes.c_void_p * self.world)(*[ptrs[r] for r in order])
+        self._view = _tensor_from_ptr(own.value, (M, N), self.device)
+        dist.barrier(group=group)  # every rank has mapped every matrix before anyone writes
+
+    def run(self, x_q: torch.Tensor, w_q_shard: torch.Tensor, x_scale: torch.Tensor, w_scale_shard: torch.Tensor,
+            barrier: bool = True) -> torch.Tensor:
+        """Launches the GEMM on the current stream; with `barrier` also the cross-rank barrier after which the
+        returned [M, N] bf16 tensor (this rank's matrix) is complete."""
+        import torch.distributed as dist
+
+        M, K = x_q.shape
+        n_local = w_q_shard.shape[0]
+        if M != self.M or n_local != self.hi - self.lo:
+            raise ValueError("operand shapes do not match the gather buffers")
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._C.gi8_matmul_blockwise_allgather(
+            x_q.data_ptr(), w_q_shard.data_ptr(), x_scale.data_ptr(), x_scale.stride(0), w_scale_shard.data_ptr(),
+            w_scale_shard.stride(0), self._outs, self.world, M, n_local, K, self.N, self.lo, stream)
+        self._lib.check(self._C, rc)
+        if barrier:
+            dist.barrier(group=self.group)
+        return self._view
+
+    def result(self) -> torch.Tensor:
+        return self._view
+
+    def close(self) -> None:
+        """Unmaps the peers' matrices and frees this rank's (collective: every rank must call it)."""
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for p in self._mapped:
+            self._lib.check(self._C, self._C.gi8_peer_release(p))
+        self._mapped = []
+        self._view = None
+        dist.barrier(group=self.group)  # nobody frees while a peer still has the matrix mapped
+        if self._own is not None:
+            self._lib.check(self._C, self._C.gi8_peer_free(self._own))
+            self._own = None
+
+
+def _tensor_from_ptr(ptr: int, shape, device: torch.device) -> torch.Tensor:
+    """A bf16 tensor over device memory the library allocated (kept alive by its owner, not by the tensor)."""
+    n = 1
+    for d in shape:
+        n *= d
+
+    class _Mem:
+        __cuda_array_interface__ = {"shape": (n,), "typestr": "<i2", "data": (ptr, False), "version": 3}
+
+    return torch.as_tensor(_Mem(), device=device).view(torch.bfloat16).view(*shape)

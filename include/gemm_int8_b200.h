@@ -113,6 +113,35 @@ int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, 
                              int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * N-sharded form of gi8_matmul_blockwise with the all-gather fused into the epilogue (no reference counterpart; the
+ * reference is single-GPU).  This rank holds rows [col0, col0 + N) of the weight (y [N,K], sw [ceil(N/128), ...]) and
+ * computes columns [col0, col0 + N) of the full [M, n_total] result; every 32 x 32 output block is written by TMA
+ * store into ALL `n_outs` matrices `outs[i]` (bf16 [M, n_total], row-major, 16-byte aligned): this rank's own and
+ * every peer's, the peers' through pointers that map their memory into this process (gi8_peer_import, or any other
+ * peer mapping the host already has).  The transfer over NVLink overlaps the GEMM tile by tile; there is no separate
+ * collective and no permuting copy.  After the call has completed on every rank (a barrier the host provides), every
+ * matrix holds the full result.  col0 and N must be multiples of 32 (N may be ragged only at the end of n_total),
+ * n_total a multiple of 8, n_outs <= 8.  Plain unicast stores only (no multicast).
+ */
+int gi8_matmul_blockwise_allgather(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                                   int64_t ld_sw, void* const* outs, int n_outs, int64_t M, int64_t N, int64_t K,
+                                   int64_t n_total, int64_t col0, void* stream);
+
+/*
+ * Peer buffers for gi8_matmul_blockwise_allgather, for hosts without peer-memory plumbing of their own:
+ *   gi8_peer_alloc / gi8_peer_free     a device allocation of its own (cudaMalloc), which an IPC handle can name
+ *   gi8_peer_export                    writes the allocation's 64-byte CUDA IPC handle
+ *   gi8_peer_import / gi8_peer_release maps / unmaps another process's allocation from its handle (peer access is
+ *                                      enabled on first use)
+ * These allocate and map memory: call them at set-up time, not per GEMM.
+ */
+int gi8_peer_alloc(void** ptr, int64_t bytes);
+int gi8_peer_free(void* ptr);
+int gi8_peer_export(void* ptr, void* handle64);
+int gi8_peer_import(const void* handle64, void** ptr);
+int gi8_peer_release(void* ptr);
+
+/*
  * Activation quantisers that feed the W8A8 entry points (the reference ships none; its benchmark only rounds and
  * clamps, benchmark.py:17-18).  Rule: s = amax / 127 (s = 1 where the block is all zero),
  * q = clamp(round_half_even(v / s), -127, 127).  `in` is row-major [M,K], fp32 (in_dtype 0) or bf16 (in_dtype 1),
