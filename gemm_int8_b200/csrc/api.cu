@@ -180,14 +180,15 @@ int ensure_smem(DeviceState* st, int slot, Kernel kernel, size_t bytes)
 
 // Tensor map over the bf16 output [M, N] (row stride ldo elements) for the epilogue's TMA stores: 32 x 32 boxes,
 // 64-byte swizzle.
-int make_output_map(CUtensorMap* map, void* out, int64_t M, int64_t N, int64_t ldo)
+int make_output_map(CUtensorMap* map, void* out, int64_t M, int64_t N, int64_t ldo, int box_cols = 32)
 {
     cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
     cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldo) * 2};
-    cuuint32_t box[2] = {32, 32};
+    cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), 32};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                          CU_TENSOR_MAP_L2_PROMOTION_NONE,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(GI8_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
     return GI8_OK;
@@ -835,6 +836,10 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         default: bn = pick_bn(M, N, st->sm_count, true);
     }
     if (gather && bn == 64) bn = 128;  // the narrow tile has no TMA-store epilogue
+    // Gathering form on the 256-wide tile: 32 x 64 store boxes (128-byte rows for NVLink), three pipeline stages to
+    // make room for the larger staging blocks.  GEMM_INT8_GATHER_BOX=32 keeps the narrow boxes.
+    bool wide = gather && bn == 256 && col0 % 64 == 0;
+    if (const char* e = getenv("GEMM_INT8_GATHER_BOX")) wide = wide && atoi(e) != 32;
     p.tiles_m = (int)((M + kBM - 1) / kBM);
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.group_m = pick_group_m(p.K);
@@ -843,7 +848,7 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     OutputMaps mo{};
     if (gather) {
         for (int i = 0; i < n_out; ++i)
-            if (int rc = make_output_map(&mo.m[i], gather[i], M, n_total, n_total)) return rc;
+            if (int rc = make_output_map(&mo.m[i], gather[i], M, n_total, n_total, wide ? 64 : 32)) return rc;
         p.tma_store = 1, p.n_out = n_out, p.out_col0 = static_cast<int>(col0);
     } else {
         const char* ts = getenv("GEMM_INT8_TMA_STORE");
@@ -865,10 +870,11 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     if (const char* e = getenv("GEMM_INT8_HALVES")) split = atoi(e) == 1 ? 1 : 2;
     if (make_operand_map(&my, y, N, K, bn)) return GI8_ERR_CUDA;
 #define GI8_LAUNCH_BW(BN_, ST_, PR_, SLOT_) GI8_LAUNCH_BWP(BN_, ST_, PR_, PIPE_X16_DOUBLE, 1, SLOT_)
-#define GI8_LAUNCH_BWP(BN_, ST_, PR_, PIPE_, SPLIT_, SLOT_)                                  \
+#define GI8_LAUNCH_BWP(BN_, ST_, PR_, PIPE_, SPLIT_, SLOT_) GI8_LAUNCH_BWS(BN_, ST_, PR_, PIPE_, SPLIT_, 32, SLOT_)
+#define GI8_LAUNCH_BWS(BN_, ST_, PR_, PIPE_, SPLIT_, SW_, SLOT_)                             \
     do {                                                                                     \
-        constexpr size_t smem = ST_ * (kBM + BN_) * kBK + kPromoWarps * 2048 + 1024;         \
-        auto kernel = blockwise_gemm_kernel<BN_, ST_, PR_, PIPE_, SPLIT_>;                   \
+        constexpr size_t smem = ST_ * (kBM + BN_) * kBK + kPromoWarps * (SW_ * 64) + 1024;   \
+        auto kernel = blockwise_gemm_kernel<BN_, ST_, PR_, PIPE_, SPLIT_, SW_>;              \
         if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                        \
         kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, mo, p);                         \
     } while (0)
@@ -876,7 +882,9 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
 #ifndef GI8_ENABLE_ABLATIONS
     if (promo > PROMO_I2F && promo != PROMO_BIAS_X2) promo = PROMO_BIAS_X2;  // ablation kernels: tuning builds only
 #endif
-    if (bn == 256) {
+    if (wide) {
+        GI8_LAUNCH_BWS(256, 3, PROMO_BIAS_X2, PIPE_X16_SINGLE, 2, 64, 52);
+    } else if (bn == 256) {
         if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC, 13);
         else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC_X2, 14);
 #ifdef GI8_ENABLE_ABLATIONS
@@ -908,6 +916,7 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     }
 #undef GI8_LAUNCH_BW
 #undef GI8_LAUNCH_BWP
+#undef GI8_LAUNCH_BWS
     GI8_CUDA(cudaGetLastError());
     return GI8_OK;
 }

@@ -159,13 +159,17 @@ enum PartialPipe : int { PIPE_X16_DOUBLE = 0, PIPE_X32_DOUBLE = 1, PIPE_X32_SING
 // MMA time earlier and run out of phase with those of the second half, and the time from "partial buffer handed
 // back" to "next partial published" -- which, with two buffers, bounds the K-block period together with the
 // promotion time -- shrinks by the MMA time of the other half.
-template <int BN, int STAGES, int PROMO, int PIPE = PIPE_X16_DOUBLE, int SPLIT = 1>
+// STORE_W: columns of one TMA-store box of the epilogue.  32: 32 rows x 64 bytes, 64-byte swizzle (2 KB of staging
+// per promotion warp).  64 (needs 64 columns per warp, i.e. BN = 256): 32 rows x 128 bytes, 128-byte swizzle (4 KB
+// per warp) -- half as many stores with rows twice as long, which is what stores that cross NVLink want.
+template <int BN, int STAGES, int PROMO, int PIPE = PIPE_X16_DOUBLE, int SPLIT = 1, int STORE_W = 32>
 __global__ void __launch_bounds__(kBlockwiseThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                       const __grid_constant__ OutputMaps outs, const BlockwiseParams p)
 {
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
     static_assert(SPLIT == 1 || (SPLIT == 2 && BN == 256), "column halves only for the 256-wide tile");
+    static_assert(STORE_W == 32 || (STORE_W == 64 && BN == 256), "wide store boxes need 64 columns per warp");
     constexpr int NBUF = 512 / BN;  // partial buffers in tensor memory (2, 4 or 8)
     constexpr int NSUB = BN / SPLIT;  // N of one MMA
     constexpr int CW = BN / 4;      // columns per promotion warp (64, 32 or 16)
@@ -282,9 +286,10 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             // Issuing the four MMAs of a K block and committing them costs one thread several hundred cycles
             // (more when its scheduler is busy with promotion warps), which is of the order of the tensor-core
             // time of the block itself.  Two threads on different schedulers therefore take alternate K blocks:
-            // each owns the tensor-memory buffers and pipeline stages of its parity, so no ordering between the
-            // two is needed.
-            static_assert(STAGES % 2 == 0 && NBUF % 2 == 0, "K blocks of one parity must map to stages/buffers of that parity");
+            // each owns the tensor-memory buffers of its parity, so no ordering between the two is needed.
+            // (Stages may be shared: consecutive K blocks never use the same stage, and every waiter derives the
+            // stage's phase from the running K-block index.)
+            static_assert(NBUF % 2 == 0, "K blocks of one parity must map to partial buffers of that parity");
             if (lane == 0) {
                 const uint32_t parity = warp == 1 ? 0u : 1u;
                 int my_tiles = 0;
@@ -590,7 +595,34 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     tile_coords(tile_again, p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
                     const int row0 = mb2 * kBM + quarter * 32;
                     const int col_base = nb2 * BN + cg * CW;
-                    if (row0 < p.M && col_base < p.N) {
+                    if constexpr (STORE_W == 64) {
+                        if (row0 < p.M && col_base < p.N) {
+                            const uint32_t stg = ((smem_u32(smem_raw) + 1023u) & ~1023u) + STAGES * kStageBytes + (warp - 4) * 4096;
+                            if (lane == 0) tma_store_wait_read<0>();
+                            __syncwarp();
+                            // row = lane: eight 16-byte chunks, chunk index xor (row % 8) (the 128-byte swizzle)
+#pragma unroll
+                            for (int q = 0; q < 8; ++q) {
+                                const int cq = q ^ (lane & 7);
+                                asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stg + lane * 128 + cq * 16),
+                                             "r"(pack_bf16x2(acc[8 * q], acc[8 * q + 1])),
+                                             "r"(pack_bf16x2(acc[8 * q + 2], acc[8 * q + 3])),
+                                             "r"(pack_bf16x2(acc[8 * q + 4], acc[8 * q + 5])),
+                                             "r"(pack_bf16x2(acc[8 * q + 6], acc[8 * q + 7]))
+                                             : "memory");
+                            }
+                            fence_proxy_async_smem();
+                            __syncwarp();
+                            if (lane == 0) {
+                                for (int o = 0; o < p.n_out; ++o)
+                                    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                                     reinterpret_cast<uint64_t>(&outs.m[o])),
+                                                 "r"(stg), "r"(p.out_col0 + col_base), "r"(row0)
+                                                 : "memory");
+                                tma_store_commit();
+                            }
+                        }
+                    } else if (row0 < p.M && col_base < p.N) {
                         const uint32_t stg = ((smem_u32(smem_raw) + 1023u) & ~1023u) + STAGES * kStageBytes + (warp - 4) * 2048;
 #pragma unroll
                         for (int c = 0; c < CW; c += 32) {
