@@ -244,6 +244,8 @@ def main():
     ap.add_argument("--K", type=int, default=0, help="override the workload's K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="nshard workload: all-gather fused into the GEMM epilogue (peer stores), or NCCL after it")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -306,9 +308,15 @@ def main():
     if nshard and world > 1:
         from gemm_int8_b200 import dist as gdist
 
-        gather_out = torch.empty((world, M, n_local), dtype=torch.bfloat16, device=dev)
-        inner = op
-        op = lambda s: gdist.all_gather_slices(inner(s), gather_out)  # noqa: E731
+        if args.gather == "fused":
+            # every rank's kernel writes its column slice into every rank's full [M, N] matrix; the step ends with
+            # the barrier after which that matrix is complete
+            fused = gdist.FusedGatherGemm(M, N)
+            op = lambda s: fused.run(s[0], s[1], s[2], s[3])  # noqa: E731
+        else:
+            gather_out = torch.empty((world, M, n_local), dtype=torch.bfloat16, device=dev)
+            inner = op
+            op = lambda s: gdist.all_gather_slices(inner(s), gather_out)  # noqa: E731
 
     def timed_steps(n):
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(n)]
@@ -374,7 +382,7 @@ def main():
     if not args.no_e2e:
         host_in = [t.pin_memory() for t in inputs]
         # N-shard: every rank reads back the gathered result ([world, M, N/world], the collective's block layout)
-        out_shape = (world, M, n_local) if (nshard and world > 1) else (M, n_local)
+        out_shape = ((M, N) if args.gather == "fused" else (world, M, n_local)) if (nshard and world > 1) else (M, n_local)
         host_out = torch.empty(out_shape, dtype=torch.bfloat16).pin_memory()
         h2d = sum(t.numel() * t.element_size() for t in host_in)
         d2h = host_out.numel() * host_out.element_size()
@@ -457,7 +465,7 @@ def main():
                        "variant": g.pick_variant({"blockwise": 2, "scaled": 1}.get(kind, 0), M, n_local, K),
                        "l2": (f"CUDA-graph replay over {copies} rotating operand copies (> 2 x L2 in total), no flush"
                               if use_graph else
-                              f"flushed between steps (256 MiB read) and operands rotated over {copies} copies"), "parallelism": f"dp{world}" if not nshard else f"nshard{world}+allgather",
+                              f"flushed between steps (256 MiB read) and operands rotated over {copies} copies"), "parallelism": f"dp{world}" if not nshard else f"nshard{world}+allgather({args.gather if world > 1 else 'none'})",
                        "frac_of_nominal_int8_peak_4500": tops / world / 4500.0 if not nshard else None},
             "roofline": roofline,
             "cpu_baseline": cb,
