@@ -840,6 +840,15 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     // make room for the larger staging blocks.  GEMM_INT8_GATHER_BOX=32 keeps the narrow boxes.
     bool wide = gather && bn == 256 && col0 % 64 == 0;
     if (const char* e = getenv("GEMM_INT8_GATHER_BOX")) wide = wide && atoi(e) != 32;
+    // The ordinary form uses the wide boxes too (measured +3-5 % on the K = 4096 prefill shape, +-2 % elsewhere);
+    // GEMM_INT8_STORE_BOX=32 (or GEMM_INT8_TMA_STORE=0, or a non-default promotion mode) keeps the four-stage kernel.
+    if (!gather && bn == 256 && p.vec_ok) {
+        const char* e = getenv("GEMM_INT8_STORE_BOX");
+        const char* ts = getenv("GEMM_INT8_TMA_STORE");
+        const char* pr = getenv("GEMM_INT8_PROMOTION");
+        const char* hv = getenv("GEMM_INT8_HALVES");
+        wide = !(e && atoi(e) == 32) && !(ts && ts[0] == '0') && !(pr && atoi(pr) != PROMO_BIAS_X2) && !(hv && atoi(hv) == 1);
+    }
     p.tiles_m = (int)((M + kBM - 1) / kBM);
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.group_m = pick_group_m(p.K);
@@ -852,9 +861,9 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         p.tma_store = 1, p.n_out = n_out, p.out_col0 = static_cast<int>(col0);
     } else {
         const char* ts = getenv("GEMM_INT8_TMA_STORE");
-        p.tma_store = p.vec_ok && !(ts && ts[0] == '0');
+        p.tma_store = p.vec_ok && (wide || !(ts && ts[0] == '0'));
         if (p.tma_store)
-            if (int rc = make_output_map(&mo.m[0], out, M, N, N)) return rc;
+            if (int rc = make_output_map(&mo.m[0], out, M, N, N, wide ? 64 : 32)) return rc;
     }
     // Tuning knobs (not part of the ABI; every combination gives bit-identical results):
     //   GEMM_INT8_PROMOTION = 0 | 1 | 2 | 9   promotion arithmetic (default 9, the biased accumulator; 3..8 are
