@@ -54,6 +54,17 @@ def test_host_side_validation_without_gpu():
     assert C.gi8_matmul_i32(p(base), p(base), p(base + 2), 8, 8, 16, None) == 3
     assert C.gi8_force_variant(b"nonsense") == 1
     assert C.gi8_force_variant(b"dense_bn128") == 0 and C.gi8_force_variant(None) == 0
+    # gathering form: argument checks come before any device work
+    outs = (ctypes.c_void_p * 2)(base, base)
+    args = (p(base), p(base), p(base), 1, p(base), 1)
+    assert C.gi8_matmul_blockwise_allgather(*args, outs, 0, 8, 32, 128, 64, 0, None) == 1    # no outputs
+    assert C.gi8_matmul_blockwise_allgather(*args, outs, 9, 8, 32, 128, 64, 0, None) == 1    # more than 8 ranks
+    assert C.gi8_matmul_blockwise_allgather(*args, outs, 2, 8, 32, 128, 64, 16, None) == 2   # slice start % 32
+    assert C.gi8_matmul_blockwise_allgather(*args, outs, 2, 8, 32, 128, 48, 32, None) == 2   # slice past n_total
+    assert b"column slice" in C.gi8_last_error()
+    bad = (ctypes.c_void_p * 2)(base, base + 2)
+    assert C.gi8_matmul_blockwise_allgather(*args, bad, 2, 8, 32, 128, 64, 0, None) == 3     # misaligned peer matrix
+    assert C.gi8_peer_alloc(None, 16) == 1 and C.gi8_peer_export(None, None) == 1 and C.gi8_peer_import(None, None) == 1
 
 
 def test_ops_registered_under_reference_names():
