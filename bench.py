@@ -244,8 +244,10 @@ def main():
     ap.add_argument("--K", type=int, default=0, help="override the workload's K")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
-                    help="nshard workload: all-gather fused into the GEMM epilogue (peer stores), or NCCL after it")
+    ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
+                    help="nshard workload: all-gather fused into the GEMM epilogue (peer stores), or NCCL after it; "
+                         "auto = fused on 2 GPUs (measured faster), NCCL on more (the fused form needs its opt-in "
+                         "wide store boxes to win there)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -279,6 +281,8 @@ def main():
     M, N, K, kind = WORKLOADS[name]
     inputs, _ = make_inputs(name, world, rank)
     nshard = name == "nshard"
+    if args.gather == "auto":
+        args.gather = "fused" if world == 2 else "nccl"
     if nshard:
         from gemm_int8_b200 import dist as gdist
 

@@ -836,18 +836,15 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         default: bn = pick_bn(M, N, st->sm_count, true);
     }
     if (gather && bn == 64) bn = 128;  // the narrow tile has no TMA-store epilogue
-    // Gathering form on the 256-wide tile: 32 x 64 store boxes (128-byte rows for NVLink), three pipeline stages to
-    // make room for the larger staging blocks.  GEMM_INT8_GATHER_BOX=32 keeps the narrow boxes.
-    bool wide = gather && bn == 256 && col0 % 64 == 0;
-    if (const char* e = getenv("GEMM_INT8_GATHER_BOX")) wide = wide && atoi(e) != 32;
-    // The ordinary form uses the wide boxes too (measured +3-5 % on the K = 4096 prefill shape, +-2 % elsewhere);
-    // GEMM_INT8_STORE_BOX=32 (or GEMM_INT8_TMA_STORE=0, or a non-default promotion mode) keeps the four-stage kernel.
+    // 32 x 64 store boxes (128-byte rows, which NVLink wants) with three pipeline stages to make room for the larger
+    // staging blocks: opt-in only.  The three-stage kernel measured 2.74 ms against 4.13 ms for the fused gather on
+    // 8 GPUs and +3-5 % on the K = 4096 prefill shape, but it faulted on one shape of the ordinary form (M = 128,
+    // N = 57344, K = 8192; cause not found), so it stays off by default: GEMM_INT8_GATHER_BOX=64 / GEMM_INT8_STORE_BOX=64.
+    bool wide = false;
+    if (const char* e = getenv("GEMM_INT8_GATHER_BOX")) wide = gather && bn == 256 && col0 % 64 == 0 && atoi(e) == 64;
     if (!gather && bn == 256 && p.vec_ok) {
         const char* e = getenv("GEMM_INT8_STORE_BOX");
-        const char* ts = getenv("GEMM_INT8_TMA_STORE");
-        const char* pr = getenv("GEMM_INT8_PROMOTION");
-        const char* hv = getenv("GEMM_INT8_HALVES");
-        wide = !(e && atoi(e) == 32) && !(ts && ts[0] == '0') && !(pr && atoi(pr) != PROMO_BIAS_X2) && !(hv && atoi(hv) == 1);
+        wide = e && atoi(e) == 64;
     }
     p.tiles_m = (int)((M + kBM - 1) / kBM);
     p.tiles_n = (int)((N + bn - 1) / bn);
