@@ -287,8 +287,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             // (more when its scheduler is busy with promotion warps), which is of the order of the tensor-core
             // time of the block itself.  Two threads on different schedulers therefore take alternate K blocks:
             // each owns the tensor-memory buffers of its parity, so no ordering between the two is needed.
-            // (Stages may be shared: consecutive K blocks never use the same stage, and every waiter derives the
-            // stage's phase from the running K-block index.)
+            // (With an odd number of stages the two issuers share every stage; see the extra wait below.)
             static_assert(NBUF % 2 == 0, "K blocks of one parity must map to partial buffers of that parity");
             if (lane == 0) {
                 const uint32_t parity = warp == 1 ? 0u : 1u;
@@ -304,6 +303,16 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     // can be prepared, so that nothing but the MMAs stands between the buffer hand-back and the
                     // tensor core.
                     [[maybe_unused]] const long long c0 = GI8_BW_CLOCK();
+                    if constexpr (STAGES % 2 != 0) {
+                        // Odd stage count: this thread's K blocks do not return to a stage with alternating parity
+                        // (stage 0 serves K blocks 0, 3, 6, ...: this thread sees only every second of its phases), and
+                        // a parity wait cannot tell phase k from phase k - 2.  Observing the other issuer's K block
+                        // first makes the thread see every phase of every stage in order.
+                        if (it >= 1 && !wait_or_abort(&bar_full[(it - 1) % STAGES], ((it - 1) / STAGES) & 1, &abort_flag)) {
+                            raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
+                            break;
+                        }
+                    }
                     const bool w1 = wait_or_abort(&bar_full[s], ph, &abort_flag);
                     const uint32_t tmem_d = tmem_base + buf * BN;
                     const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
