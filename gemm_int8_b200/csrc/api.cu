@@ -837,11 +837,11 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     }
     if (gather && bn == 64) bn = 128;  // the narrow tile has no TMA-store epilogue
     // 32 x 64 store boxes (128-byte rows, which NVLink wants) with three pipeline stages to make room for the larger
-    // staging blocks: opt-in only.  The three-stage kernel measured 2.74 ms against 4.13 ms for the fused gather on
-    // 8 GPUs and +3-5 % on the K = 4096 prefill shape, but it faulted on one shape of the ordinary form (M = 128,
-    // N = 57344, K = 8192; cause not found), so it stays off by default: GEMM_INT8_GATHER_BOX=64 / GEMM_INT8_STORE_BOX=64.
-    bool wide = false;
-    if (const char* e = getenv("GEMM_INT8_GATHER_BOX")) wide = gather && bn == 256 && col0 % 64 == 0 && atoi(e) == 64;
+    // staging blocks.  Default for the gathering form on the 256-wide tile (2.74 ms against 4.13 ms on 8 GPUs;
+    // GEMM_INT8_GATHER_BOX=32 keeps the four-stage kernel); opt-in for the ordinary form (GEMM_INT8_STORE_BOX=64:
+    // +3-5 % on the K = 4096 prefill shape, +-2 % elsewhere).
+    bool wide = gather && bn == 256 && col0 % 64 == 0;
+    if (const char* e = getenv("GEMM_INT8_GATHER_BOX")) wide = wide && atoi(e) != 32;
     if (!gather && bn == 256 && p.vec_ok) {
         const char* e = getenv("GEMM_INT8_STORE_BOX");
         wide = e && atoi(e) == 64;
