@@ -350,7 +350,8 @@ def quantize_per_token(a: torch.Tensor):
 
 
 def force_variant(name: str | None) -> None:
-    """Force a kernel variant ("dense_bn256", "dense_bn128", "dense_bn64", "smallm"); None = fitted dispatch."""
+    """Force a kernel variant ("dense_bn256", "dense_bn128", "dense_bn64", "pair", "smallm", "smallm_cluster");
+    None = fitted dispatch."""
     _lib.check(_C, _C.gi8_force_variant(name.encode() if name else None))
 
 
@@ -360,10 +361,30 @@ def pick_variant(kind: int, M: int, N: int, K: int) -> str:
 
 
 def device_status() -> int:
-    """Synchronises the current device and returns (then clears) its kernel status word; 0 = healthy."""
+    """Synchronises the current device and returns (then clears) its kernel status word; 0 = healthy.
+
+    A non-zero word means a kernel gave up a bounded wait and may have left the split-K scratch of the
+    "smallm" variant half-summed, so the cached scratch buffers are dropped (the next call allocates zeroed ones)."""
     code = ctypes.c_uint32(0)
     _lib.check(_C, _C.gi8_device_status(ctypes.byref(code)))
+    if code.value:
+        _workspaces.clear()
     return int(code.value)
+
+
+def check_device() -> None:
+    """Synchronises the current device and raises GemmInt8Error (GI8_ERR_DEVICE_TIMEOUT) if a kernel since the
+    last check gave up a bounded wait -- the counterpart of the reference's exception on a failed launch
+    (csrc/kernels/gemm.cu:108-121)."""
+    rc = _C.gi8_device_check()
+    if rc:
+        _workspaces.clear()
+    _lib.check(_C, rc)
+
+
+def reload_env() -> None:
+    """Re-reads the GEMM_INT8_* tuning variables (they are otherwise read once, at first use)."""
+    _lib.check(_C, _C.gi8_reload_env())
 
 
 # GEMM_INT8_KERNEL=<variant> forces a kernel variant for the whole process (tuning and profiling).
@@ -376,4 +397,4 @@ if _os.environ.get("GEMM_INT8_KERNEL"):
 from .linear import Int8Linear  # noqa: E402
 
 __all__ = ["matmul", "matmul_i32", "matmul_scaled", "matmul_blockwise", "quantize_per_token_block",
-           "quantize_per_token", "Int8Linear", "force_variant", "pick_variant", "device_status"]
+           "quantize_per_token", "Int8Linear", "force_variant", "pick_variant", "device_status", "check_device", "reload_env"]

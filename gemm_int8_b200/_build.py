@@ -13,7 +13,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libgemm_int8_b200.so"
 LIB_PATH = os.path.join(_PKG, LIB_NAME)
 SOURCES = [os.path.join(_PKG, "csrc", "api.cu")]
-HEADERS = [os.path.join(_PKG, "csrc", f) for f in ("ptx.cuh", "k_dense.cuh", "k_blockwise.cuh", "k_blockwise2.cuh", "k_smallm.cuh", "k_quant.cuh", "k_gemv.cuh")]
+HEADERS = [os.path.join(_PKG, "csrc", f) for f in ("ptx.cuh", "k_dense.cuh", "k_blockwise.cuh", "k_smallm.cuh", "k_quant.cuh")]
 HEADERS.append(os.path.join(os.path.dirname(_PKG), "include", "gemm_int8_b200.h"))
 
 NVCC_FLAGS = [
@@ -42,8 +42,6 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not is_stale():
         return LIB_PATH
     cmd = [_nvcc(), *NVCC_FLAGS, "-o", LIB_PATH, *SOURCES]
-    if os.environ.get("GI8_ABLATIONS") == "1":  # tuning builds only: adds measurement kernels with wrong results
-        cmd.insert(1, "-DGI8_ENABLE_ABLATIONS")
     if verbose:
         cmd.insert(1, "-Xptxas")
         cmd.insert(2, "-v")

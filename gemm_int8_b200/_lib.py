@@ -45,6 +45,9 @@ SYMBOLS = {
     "gi8_force_variant": (_i, [ctypes.c_char_p]),
     "gi8_pick_variant": (ctypes.c_char_p, [_i, _i64, _i64, _i64]),
     "gi8_device_status": (_i, [ctypes.POINTER(ctypes.c_uint32)]),
+    "gi8_device_check": (_i, []),
+    "gi8_selftest_wait_timeout": (_i, [_p]),
+    "gi8_reload_env": (_i, []),
 }
 
 

@@ -8,13 +8,12 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
 #include "k_blockwise.cuh"
-#include "k_blockwise2.cuh"
 #include "k_dense.cuh"
-#include "k_gemv.cuh"
 #include "k_quant.cuh"
 #include "k_smallm.cuh"
 
@@ -45,10 +44,51 @@ int fail(int code, const char* fmt, ...)
 // Kernel status word: one instance per device (module-scope device variable).
 __device__ uint32_t g_kernel_status;
 
-enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM, VAR_SMALLM_CLUSTER, VAR_PAIR, VAR_GEMV };
-const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "smallm_cluster", "pair", "gemv"};
-constexpr int kNumVariants = 8;
-int g_forced_variant = VAR_AUTO;
+enum Variant : int { VAR_AUTO = 0, VAR_DENSE_BN256, VAR_DENSE_BN128, VAR_DENSE_BN64, VAR_SMALLM, VAR_SMALLM_CLUSTER, VAR_PAIR };
+const char* const kVariantNames[] = {"auto", "dense_bn256", "dense_bn128", "dense_bn64", "smallm", "smallm_cluster", "pair"};
+constexpr int kNumVariants = 7;
+std::atomic<int> g_forced_variant{VAR_AUTO};
+
+// Tuning knobs from the environment (not part of the ABI; every combination gives bit-identical results).  They are
+// read once, when the library is first used, and again only when gi8_reload_env() is called: nothing on the launch
+// path calls getenv.
+//   GEMM_INT8_GROUP_M    = 1..64   row-blocks per rasterisation band (default: fitted to K)
+//   GEMM_INT8_TMA_STORE  = 0       bf16 epilogues store from registers instead of through shared memory + TMA
+//   GEMM_INT8_PDL        = 0       small-M kernels are launched without programmatic dependent launch
+//   GEMM_INT8_SPLITS     = n       small-M kernels: number of K splits
+//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256, or two column halves with N = 128
+//   GEMM_INT8_BW_ISSUERS = 1 | 2   blockwise kernel: MMA-issuing threads
+struct Knobs {
+    int group_m = 0;
+    bool tma_store = true;
+    bool pdl = true;
+    int splits = 0;
+    int bw_halves = 1;
+    int bw_issuers = 1;
+};
+Knobs g_knobs;
+std::once_flag g_knobs_once;
+
+void load_knobs()
+{
+    Knobs k;
+    if (const char* e = getenv("GEMM_INT8_GROUP_M")) {
+        const int v = atoi(e);
+        if (v >= 1 && v <= 64) k.group_m = v;
+    }
+    if (const char* e = getenv("GEMM_INT8_TMA_STORE")) k.tma_store = e[0] != '0';
+    if (const char* e = getenv("GEMM_INT8_PDL")) k.pdl = e[0] != '0';
+    if (const char* e = getenv("GEMM_INT8_SPLITS")) k.splits = atoi(e);
+    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 2 ? 2 : 1;
+    if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 2 ? 2 : 1;
+    g_knobs = k;
+}
+
+const Knobs& knobs()
+{
+    std::call_once(g_knobs_once, load_knobs);
+    return g_knobs;
+}
 
 struct DeviceState {
     bool ready = false;
@@ -97,19 +137,70 @@ int get_device_state(DeviceState** out)
     return GI8_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------
+// Tensor-map cache.  A tensor map is a pure function of (base pointer, extents, row stride, box, element type), so a
+// map built once can be reused for every later call with the same key -- a decode loop calls with the same weight
+// pointers thousands of times, and encoding two to ten maps per call is a measurable part of a 6 us kernel.  A stale
+// entry cannot be wrong: the same key always encodes to the same descriptor, whatever happened to the memory since.
+// 4-way set-associative, 256 sets, guarded by g_mutex; replacement is round-robin within the set.
+// ---------------------------------------------------------------------------------------------------
+struct MapKey {
+    const void* base;
+    uint64_t d0, d1, stride_bytes;
+    uint32_t box0, box1, kind;  // kind: 0 = int8 operand, 1 = bf16 output
+    bool operator==(const MapKey& o) const
+    {
+        return base == o.base && d0 == o.d0 && d1 == o.d1 && stride_bytes == o.stride_bytes && box0 == o.box0 &&
+               box1 == o.box1 && kind == o.kind;
+    }
+};
+struct MapEntry {
+    MapKey key{};
+    bool valid = false;
+    CUtensorMap map;
+};
+constexpr int kMapSets = 256, kMapWays = 4;
+MapEntry g_map_cache[kMapSets][kMapWays];
+uint8_t g_map_next[kMapSets] = {};
+
+int cached_map(CUtensorMap* out, const MapKey& key)
+{
+    uint64_t h = reinterpret_cast<uintptr_t>(key.base) * 0x9E3779B97F4A7C15ull;
+    h ^= (key.d0 * 0xC2B2AE3D27D4EB4Full) ^ (key.d1 * 0x165667B19E3779F9ull) ^ (key.box1 * 0x27D4EB2Full) ^ key.kind;
+    const int set = static_cast<int>((h >> 40) % kMapSets);
+    std::lock_guard<std::mutex> lock(g_mutex);
+    for (int w = 0; w < kMapWays; ++w)
+        if (g_map_cache[set][w].valid && g_map_cache[set][w].key == key) {
+            *out = g_map_cache[set][w].map;
+            return GI8_OK;
+        }
+    cuuint64_t dims[2] = {key.d0, key.d1};
+    cuuint64_t strides[1] = {key.stride_bytes};
+    cuuint32_t box[2] = {key.box0, key.box1};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r;
+    if (key.kind == 0)
+        r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(key.base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    else
+        r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(key.base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, key.box0 == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                     CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(GI8_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+    MapEntry& e = g_map_cache[set][g_map_next[set]];
+    g_map_next[set] = static_cast<uint8_t>((g_map_next[set] + 1) % kMapWays);
+    e.key = key, e.map = *out, e.valid = true;
+    return GI8_OK;
+}
+
 // Tensor map over a row-major int8 matrix [rows, K]: dimension 0 = K (contiguous), dimension 1 = rows.
 // Box = 128 bytes of K x box_rows rows, 128-byte swizzle, out-of-range elements read as zero.
 int make_operand_map(CUtensorMap* map, const int8_t* base, int64_t rows, int64_t K, int box_rows)
 {
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(rows)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(K)};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), static_cast<cuuint32_t>(box_rows)};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<int8_t*>(base), dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(GI8_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
-    return GI8_OK;
+    MapKey key{base, static_cast<uint64_t>(K), static_cast<uint64_t>(rows), static_cast<uint64_t>(K),
+               static_cast<uint32_t>(kBK), static_cast<uint32_t>(box_rows), 0u};
+    return cached_map(map, key);
 }
 
 int check_common(const void* x, const void* y, const void* out, int64_t M, int64_t N, int64_t K, int out_align)
@@ -155,13 +246,9 @@ int pick_bn(int64_t M, int64_t N, int sms, bool blockwise)
 
 // Rasterisation band height in row-blocks: the band's slice of x (group_m x 128 x K bytes) is kept near 16 MB so
 // that it stays in L2 while the band sweeps over y (fitted on 8192^3, 16384^3 and the K = 4096 layer shapes).
-// GEMM_INT8_GROUP_M overrides it for tuning.
 int pick_group_m(int64_t K)
 {
-    if (const char* e = getenv("GEMM_INT8_GROUP_M")) {
-        const int v = atoi(e);
-        if (v >= 1 && v <= 64) return v;
-    }
+    if (knobs().group_m) return knobs().group_m;
     int64_t g = (16ll << 20) / (kBM * (K > 0 ? K : 1));
     if (g < 4) g = 4;
     if (g > 32) g = 32;
@@ -171,6 +258,7 @@ int pick_group_m(int64_t K)
 template <typename Kernel>
 int ensure_smem(DeviceState* st, int slot, Kernel kernel, size_t bytes)
 {
+    std::lock_guard<std::mutex> lock(g_mutex);
     if (!st->attr_set[slot]) {
         GI8_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)));
         st->attr_set[slot] = true;
@@ -178,20 +266,13 @@ int ensure_smem(DeviceState* st, int slot, Kernel kernel, size_t bytes)
     return GI8_OK;
 }
 
-// Tensor map over the bf16 output [M, N] (row stride ldo elements) for the epilogue's TMA stores: 32 x 32 boxes,
-// 64-byte swizzle.
+// Tensor map over the bf16 output [M, N] (row stride ldo elements) for the epilogue's TMA stores: boxes of 32 rows x
+// box_cols columns, 64-byte swizzle (32 columns) or 128-byte swizzle (64 columns).
 int make_output_map(CUtensorMap* map, void* out, int64_t M, int64_t N, int64_t ldo, int box_cols = 32)
 {
-    cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
-    cuuint64_t strides[1] = {static_cast<cuuint64_t>(ldo) * 2};
-    cuuint32_t box[2] = {static_cast<cuuint32_t>(box_cols), 32};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, out, dims, strides, box, estr,
-                          CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                          CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail(GI8_ERR_CUDA, "cuTensorMapEncodeTiled (output) failed with CUresult %d", static_cast<int>(r));
-    return GI8_OK;
+    MapKey key{out, static_cast<uint64_t>(N), static_cast<uint64_t>(M), static_cast<uint64_t>(ldo) * 2,
+               static_cast<uint32_t>(box_cols), 32u, 1u};
+    return cached_map(map, key);
 }
 
 template <int BN, int STAGES, int EPI>
@@ -204,9 +285,8 @@ int launch_dense(DeviceState* st, int slot, const int8_t* x, const int8_t* y, De
     CUtensorMap mx, my, mo;
     if (int rc = make_operand_map(&mx, x, p.M, p.K, kBM)) return rc;
     if (int rc = make_operand_map(&my, y, p.N, p.K, BN)) return rc;
-    // bf16 epilogues store through TMA when the output rows are 16-byte aligned (GEMM_INT8_TMA_STORE=0: plain stores)
-    const char* ts = getenv("GEMM_INT8_TMA_STORE");
-    p.tma_store = (EPI != EPI_RAW_I32) && p.vec_ok && !(ts && ts[0] == '0');
+    // bf16 epilogues store through TMA when the output rows are 16-byte aligned
+    p.tma_store = (EPI != EPI_RAW_I32) && p.vec_ok && knobs().tma_store;
     if (p.tma_store) {
         if (int rc = make_output_map(&mo, p.out, p.M, p.N, p.ldo)) return rc;
     } else {
@@ -234,8 +314,7 @@ int launch_dense_pair(DeviceState* st, int slot, const int8_t* x, const int8_t* 
     CUtensorMap mx, my, mo;
     if (int rc = make_operand_map(&mx, x, p.M, p.K, kBM)) return rc;
     if (int rc = make_operand_map(&my, y, p.N, p.K, BN / 2)) return rc;
-    const char* ts = getenv("GEMM_INT8_TMA_STORE");
-    p.tma_store = (EPI != EPI_RAW_I32) && p.vec_ok && !(ts && ts[0] == '0');
+    p.tma_store = (EPI != EPI_RAW_I32) && p.vec_ok && knobs().tma_store;
     if (p.tma_store) {
         if (int rc = make_output_map(&mo, p.out, p.M, p.N, p.ldo)) return rc;
     } else {
@@ -265,9 +344,10 @@ int launch_dense_pair(DeviceState* st, int slot, const int8_t* x, const int8_t* 
 template <int EPI>
 int dispatch_dense(DeviceState* st, const int8_t* x, const int8_t* y, DenseParams p, cudaStream_t stream)
 {
-    if (g_forced_variant == VAR_PAIR) return launch_dense_pair<EPI>(st, 45 + EPI, x, y, p, stream);
+    const int forced = g_forced_variant;
+    if (forced == VAR_PAIR) return launch_dense_pair<EPI>(st, 45 + EPI, x, y, p, stream);
     int bn;
-    switch (g_forced_variant) {
+    switch (forced) {
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
         case VAR_DENSE_BN64: bn = 64; break;
@@ -291,65 +371,6 @@ int zero_output(void* out, int64_t bytes, cudaStream_t stream)
     fill_zero_kernel<<<148, 256, 0, stream>>>(static_cast<uint8_t*>(out), bytes);
     GI8_CUDA(cudaGetLastError());
     return GI8_OK;
-}
-
-// ---------------------------------------------------------------------------------------------------
-// Fewest tokens: the weight-streaming dp4a kernel (no tensor memory, no TMA, no set-up).  Measured against the
-// cluster split-K kernel on B200 (CUDA-graph replays over HBM-cold weights) it is 0.3-0.5 us faster at M = 1,
-// K = 4096 and slower everywhere else (M = 4: 6.9 vs 6.7 us at 4096 x 4096, 17.2 vs 13.6 us at K = 14336), so the
-// fixed cost of the decode shapes is launch and ramp-up, not the tensor-core set-up.  Kept as the selectable
-// variant "gemv"; the automatic dispatch does not use it unless GEMM_INT8_GEMV_M raises the limit.
-// ---------------------------------------------------------------------------------------------------
-constexpr int kGemvMaxM = 8;     // the kernel exists for token tiles 1, 2, 4, 8
-int g_gemv_auto_m = 0;           // the automatic dispatch uses it up to this M (GEMM_INT8_GEMV_M overrides)
-constexpr int64_t kGemvMaxSmem = 200 * 1024;
-
-template <int MT>
-int launch_gemv(DeviceState* st, int slot, const GemvParams& p, cudaStream_t stream)
-{
-    const size_t smem = static_cast<size_t>(MT) * p.K;
-    auto kernel = gemv_scaled_kernel<MT>;
-    // the opt-in limit is set once per kernel, so to the largest size any K may need
-    if (int rc = ensure_smem(st, slot, kernel, static_cast<size_t>(kGemvMaxSmem))) return rc;
-    const int warps_per_cta = kGemvThreads / 32;
-    int grid = (p.N + warps_per_cta - 1) / warps_per_cta;
-    const int cap = st->sm_count * 8;
-    if (grid > cap) grid = cap;
-    cudaLaunchConfig_t cfg{};
-    cfg.gridDim = dim3(grid, 1, 1);
-    cfg.blockDim = dim3(kGemvThreads, 1, 1);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    const char* pdl = getenv("GEMM_INT8_PDL");
-    cfg.numAttrs = (pdl && pdl[0] == '0') ? 0 : 1;
-    GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, p));
-    return GI8_OK;
-}
-
-bool gemv_applies(int64_t M, int64_t K, bool forced)
-{
-    int limit = g_gemv_auto_m;
-    if (const char* e = getenv("GEMM_INT8_GEMV_M")) limit = atoi(e);
-    if (forced) limit = kGemvMaxM;
-    if (M < 1 || M > limit || M > kGemvMaxM) return false;
-    const int mt = M <= 1 ? 1 : M <= 2 ? 2 : M <= 4 ? 4 : 8;
-    return static_cast<int64_t>(mt) * K <= kGemvMaxSmem;
-}
-
-int dispatch_gemv(DeviceState* st, const int8_t* x, const int8_t* y, const float* sx, const float* sw, void* out,
-                  int64_t M, int64_t N, int64_t K, cudaStream_t stream)
-{
-    GemvParams p{};
-    p.x = x, p.w = y, p.sx = sx, p.sw = sw, p.out = static_cast<uint16_t*>(out), p.ldo = N;
-    p.M = (int)M, p.N = (int)N, p.K = (int)K;
-    if (M <= 1) return launch_gemv<1>(st, 48, p, stream);
-    if (M <= 2) return launch_gemv<2>(st, 49, p, stream);
-    if (M <= 4) return launch_gemv<4>(st, 50, p, stream);
-    return launch_gemv<8>(st, 51, p, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------
@@ -380,8 +401,7 @@ SmallMPlan plan_smallm(int64_t M, int64_t N, int64_t K, int sms, bool forced, in
     if (splits <= 2) splits = 1;  // many weight tiles already fill the machine; a second split only adds a reduction
     if (splits > kb_total / 2) splits = kb_total / 2 > 0 ? kb_total / 2 : 1;
     if (splits > max_splits) splits = max_splits;
-    if (const char* e = getenv("GEMM_INT8_SPLITS")) {  // tuning override
-        const int v = atoi(e);
+    if (const int v = knobs().splits) {  // tuning override
         if (v >= 1 && v <= max_splits && v <= kb_total) splits = v;
     }
     pl.kb_per_split = (kb_total + splits - 1) / splits;
@@ -432,12 +452,11 @@ int launch_smallm_cluster(DeviceState* st, int slot, const int8_t* x, const int8
     attr[0].val.clusterDim.y = pl.splits;
     attr[0].val.clusterDim.z = 1;
     // Programmatic dependent launch: this kernel's set-up overlaps the tail of the previous kernel in the stream
-    // (it waits with griddepcontrol.wait before its first global access).  GEMM_INT8_PDL=0 turns it off.
+    // (it waits with griddepcontrol.wait before its first global access).
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    const char* pdl = getenv("GEMM_INT8_PDL");
-    cfg.numAttrs = (pdl && pdl[0] == '0') ? 1 : 2;
+    cfg.numAttrs = knobs().pdl ? 2 : 1;
     GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mw, mx, p));
     return GI8_OK;
 }
@@ -468,6 +487,31 @@ int get_static_scratch(void** out)
 
 }  // namespace
 
+// Exercises the bounded-wait error path without faulting or hanging anything: warp 1 waits (1 ms limit) on a barrier
+// that nobody ever arrives on, gives up, records ERR_TIMEOUT_EPILOGUE and raises the CTA's abort flag; warp 0 waits
+// on a second such barrier with the ordinary limit and must leave early because of the flag.  The kernel then
+// returns normally and the context stays usable.
+__global__ void wait_timeout_selftest_kernel(uint32_t* status)
+{
+    __shared__ __align__(8) uint64_t bar_never[2];
+    __shared__ volatile uint32_t abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        gi8::mbar_init(&bar_never[0], 1);
+        gi8::mbar_init(&bar_never[1], 1);
+        gi8::fence_barrier_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 32) {
+        if (!gi8::wait_or_abort(&bar_never[0], 0, &abort_flag, 1000000ull))
+            gi8::raise_error(status, &abort_flag, gi8::ERR_TIMEOUT_EPILOGUE);
+    } else if (threadIdx.x == 0) {
+        // returns false within microseconds of the flag being raised, long before its own 250 ms limit
+        if (gi8::wait_or_abort(&bar_never[1], 0, &abort_flag)) gi8::raise_error(status, &abort_flag, gi8::ERR_TIMEOUT_PRODUCER);
+    }
+    __syncthreads();
+}
+
 template <typename T>
 static int launch_hadamard_quant(const T* in, int8_t* q, float* scales, int64_t M, int K, int KB, int H, cudaStream_t s)
 {
@@ -490,29 +534,6 @@ static int launch_hadamard_quant(const T* in, int8_t* q, float* scales, int64_t 
 
 extern "C" {
 
-#ifdef GI8_ENABLE_ABLATIONS
-// Tuning builds only (not declared in the public header): copies out and clears the pair kernel's wait counters.
-int gi8_debug_bw_counters(unsigned long long* out, int n)
-{
-    if (n > 148 * 8) n = 148 * 8;
-    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
-    if (cudaMemcpyFromSymbol(out, gi8::g_bw_dbg, sizeof(unsigned long long) * n) != cudaSuccess) return 1;
-    static unsigned long long zeros[148 * 8] = {};
-    if (cudaMemcpyToSymbol(gi8::g_bw_dbg, zeros, sizeof(zeros)) != cudaSuccess) return 1;
-    return 0;
-}
-
-int gi8_debug_pair_counters(unsigned long long* out, int n)
-{
-    if (n > 148 * 8) n = 148 * 8;
-    if (cudaDeviceSynchronize() != cudaSuccess) return 1;
-    if (cudaMemcpyFromSymbol(out, gi8::g_pair_dbg, sizeof(unsigned long long) * n) != cudaSuccess) return 1;
-    static unsigned long long zeros[148 * 8] = {};
-    if (cudaMemcpyToSymbol(gi8::g_pair_dbg, zeros, sizeof(zeros)) != cudaSuccess) return 1;
-    return 0;
-}
-#endif
-
 int gi8_version(void) { return 100; }
 
 const char* gi8_last_error(void) { return g_err; }
@@ -533,15 +554,45 @@ int gi8_force_variant(const char* name)
 
 const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
 {
-    (void)K;
     int sms = 148;
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
-    if (g_forced_variant != VAR_AUTO) return kVariantNames[g_forced_variant];
-    if (kind == 1 && gemv_applies(M, K, false)) return "gemv";
+    DeviceState* st = nullptr;
+    if (get_device_state(&st) == GI8_OK) sms = st->sm_count;
+    const int forced = g_forced_variant;
+    if (forced != VAR_AUTO) return kVariantNames[forced];
     if (kind == 1 && plan_smallm(M, N, K, sms, false).use) return "smallm_cluster";
-    const int bn = pick_bn(M, N, sms, kind == 2);
+    if (kind == 2) {
+        const int bn = pick_bn(M, N, sms, true);
+        return bn == 256 ? "blockwise_bn256" : bn == 128 ? "blockwise_bn128" : "blockwise_bn64";
+    }
+    const int bn = pick_bn(M, N, sms, false);
     return bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
+}
+
+int gi8_reload_env(void)
+{
+    knobs();  // make sure the one-time load has happened, then load again
+    std::lock_guard<std::mutex> lock(g_mutex);
+    load_knobs();
+    return GI8_OK;
+}
+
+int gi8_device_check(void)
+{
+    uint32_t code = 0;
+    if (int rc = gi8_device_status(&code)) return rc;
+    if (code)
+        return fail(GI8_ERR_DEVICE_TIMEOUT, "a kernel gave up a bounded wait: role %u (1 producer, 2 MMA issuer, 3 epilogue, "
+                    "4 drain, 5 reduction) in CTA %u; the results of that launch are invalid", code & 0xff, code >> 8);
+    return GI8_OK;
+}
+
+int gi8_selftest_wait_timeout(void* stream)
+{
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    wait_timeout_selftest_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(st->status);
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
 }
 
 int gi8_device_status(uint32_t* code)
@@ -585,10 +636,12 @@ int gi8_matmul_i32(const int8_t* x, const int8_t* y, int32_t* out, int64_t M, in
 
 int64_t gi8_matmul_scaled_workspace_bytes(int64_t M, int64_t N, int64_t K)
 {
-    int sms = 148;
-    int dev = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sms = g_dev[dev].sm_count;
     if (g_forced_variant != VAR_SMALLM) return 0;  // only the scratch variant needs a workspace
+    // The plan depends on the SM count, so the device is initialised here: the size returned is the size the launch
+    // will ask for.
+    int sms = 148;
+    DeviceState* st = nullptr;
+    if (get_device_state(&st) == GI8_OK) sms = st->sm_count;
     const SmallMPlan pl = plan_smallm(M, N, K, sms, true);
     return pl.use ? pl.total_bytes : 0;
 }
@@ -605,10 +658,9 @@ int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const f
     if (int rc = get_device_state(&st)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (K == 0) return zero_output(out, M * N * 2, s);
-    if ((g_forced_variant == VAR_AUTO || g_forced_variant == VAR_GEMV) && gemv_applies(M, K, g_forced_variant == VAR_GEMV))
-        return dispatch_gemv(st, x, y, sx, sw, out, M, N, K, s);
-    if (g_forced_variant == VAR_AUTO || g_forced_variant == VAR_SMALLM_CLUSTER) {
-        const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, g_forced_variant == VAR_SMALLM_CLUSTER, kMaxClusterSplits);
+    const int forced = g_forced_variant;
+    if (forced == VAR_AUTO || forced == VAR_SMALLM_CLUSTER) {
+        const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, forced == VAR_SMALLM_CLUSTER, kMaxClusterSplits);
         if (pl.use) {
             SmallMParams q{};
             q.out = out, q.sx = sx, q.sw = sw, q.status = st->status, q.ldo = N;
@@ -621,7 +673,7 @@ int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const f
             }
         }
     }
-    if (g_forced_variant == VAR_SMALLM) {
+    if (forced == VAR_SMALLM) {
         const SmallMPlan pl = plan_smallm(M, N, K, st->sm_count, true);
         if (pl.use) {
             SmallMParams q{};
@@ -800,52 +852,23 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
     p.n_out = 1, p.out_col0 = 0;
-    CUtensorMap mx, my;
-    if (int rc = make_operand_map(&mx, x, M, K, kBM)) return rc;
-    if (g_forced_variant == VAR_PAIR && !gather) {
-        // Two-CTA form: 256 x 128 tiles, one CTA pair per tile.
-        if (int rc = make_operand_map(&my, y, N, K, 64)) return rc;
-        p.tiles_m = (int)((M + kPairBM - 1) / kPairBM);
-        p.tiles_n = (int)((N + 127) / 128);
-        p.group_m = pick_group_m(p.K) / 2 > 0 ? pick_group_m(p.K) / 2 : 1;
-        const int64_t tiles2 = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
-        const int pairs = static_cast<int>(tiles2 < st->sm_count / 2 ? tiles2 : st->sm_count / 2);
-        constexpr size_t smem2 = 8 * (kBM + 64) * kBK + 1024;
-        auto kernel2 = blockwise_pair_kernel<8, PROMO_I2F>;
-        if (int rc = ensure_smem(st, 23, kernel2, smem2)) return rc;
-        cudaLaunchConfig_t cfg{};
-        cfg.gridDim = dim3(2 * pairs, 1, 1);
-        cfg.blockDim = dim3(kBlockwiseThreads, 1, 1);
-        cfg.dynamicSmemBytes = smem2;
-        cfg.stream = s;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = 2;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
-        cfg.attrs = attr;
-        cfg.numAttrs = 1;
-        GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel2, mx, my, p));
-        return GI8_OK;
-    }
     int bn;
-    switch (g_forced_variant) {
+    switch (static_cast<int>(g_forced_variant)) {  // (the two-CTA variant exists for the dense kernel only)
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
         case VAR_DENSE_BN64: bn = 64; break;
         default: bn = pick_bn(M, N, st->sm_count, true);
     }
-    if (gather && bn == 64) bn = 128;  // the narrow tile has no TMA-store epilogue
-    // 32 x 64 store boxes (128-byte rows, which NVLink wants) with three pipeline stages to make room for the larger
-    // staging blocks.  Default for the gathering form on the 256-wide tile (2.74 ms against 4.13 ms on 8 GPUs;
-    // GEMM_INT8_GATHER_BOX=32 keeps the four-stage kernel); opt-in for the ordinary form (GEMM_INT8_STORE_BOX=64:
-    // +3-5 % on the K = 4096 prefill shape, +-2 % elsewhere).
-    bool wide = gather && bn == 256 && col0 % 64 == 0;
-    if (const char* e = getenv("GEMM_INT8_GATHER_BOX")) wide = wide && atoi(e) != 32;
-    if (!gather && bn == 256 && p.vec_ok) {
-        const char* e = getenv("GEMM_INT8_STORE_BOX");
-        wide = e && atoi(e) == 64;
-    }
+    // The epilogue's TMA-store boxes are 64 columns wide for the 256- and 128-wide tiles and 32 for the 64-wide one.
+    // A box is clipped at the edge of the tensor map, i.e. of the whole [M, n_total] matrix, not at the edge of this
+    // GEMM's column slice: a slice that starts or ends inside a box (and is not the last one) would overwrite its
+    // neighbour's columns, so such slices take the narrow tile, whose boxes the slice contract (multiples of 32)
+    // always fits.
+    if (gather && (col0 % 64 != 0 || (N % 64 != 0 && col0 + N != n_total))) bn = 64;
+    const int box_cols = blockwise_store_cols(bn);
+    CUtensorMap mx, my;
+    if (int rc = make_operand_map(&mx, x, M, K, kBM)) return rc;
+    if (int rc = make_operand_map(&my, y, N, K, bn)) return rc;
     p.tiles_m = (int)((M + kBM - 1) / kBM);
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.group_m = pick_group_m(p.K);
@@ -854,75 +877,37 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     OutputMaps mo{};
     if (gather) {
         for (int i = 0; i < n_out; ++i)
-            if (int rc = make_output_map(&mo.m[i], gather[i], M, n_total, n_total, wide ? 64 : 32)) return rc;
+            if (int rc = make_output_map(&mo.m[i], gather[i], M, n_total, n_total, box_cols)) return rc;
         p.tma_store = 1, p.n_out = n_out, p.out_col0 = static_cast<int>(col0);
     } else {
-        const char* ts = getenv("GEMM_INT8_TMA_STORE");
-        p.tma_store = p.vec_ok && (wide || !(ts && ts[0] == '0'));
+        p.tma_store = p.vec_ok && knobs().tma_store;
         if (p.tma_store)
-            if (int rc = make_output_map(&mo.m[0], out, M, N, N, wide ? 64 : 32)) return rc;
+            if (int rc = make_output_map(&mo.m[0], out, M, N, N, box_cols)) return rc;
     }
-    // Tuning knobs (not part of the ABI; every combination gives bit-identical results):
-    //   GEMM_INT8_PROMOTION = 0 | 1 | 2 | 9   promotion arithmetic (default 9, the biased accumulator; 3..8 are
-    //                                         measurement-only ablations with wrong results, tuning builds only)
-    //   GEMM_INT8_PIPE      = 0 | 2           with promotion 2: double-buffered 16-column (default) or single
-    //                                         32-column loads
-    //   GEMM_INT8_HALVES    = 1 | 2           256-wide tile: MMAs with N = 256, or two column halves with N = 128
-    int promo = PROMO_BIAS_X2;
-    if (const char* e = getenv("GEMM_INT8_PROMOTION")) promo = atoi(e);
-    int pipe = -1;
-    if (const char* e = getenv("GEMM_INT8_PIPE")) pipe = atoi(e);
-    int split = 2;
-    if (const char* e = getenv("GEMM_INT8_HALVES")) split = atoi(e) == 1 ? 1 : 2;
-    if (make_operand_map(&my, y, N, K, bn)) return GI8_ERR_CUDA;
-#define GI8_LAUNCH_BW(BN_, ST_, PR_, SLOT_) GI8_LAUNCH_BWP(BN_, ST_, PR_, PIPE_X16_DOUBLE, 1, SLOT_)
-#define GI8_LAUNCH_BWP(BN_, ST_, PR_, PIPE_, SPLIT_, SLOT_) GI8_LAUNCH_BWS(BN_, ST_, PR_, PIPE_, SPLIT_, 32, SLOT_)
-#define GI8_LAUNCH_BWS(BN_, ST_, PR_, PIPE_, SPLIT_, SW_, SLOT_)                             \
-    do {                                                                                     \
-        constexpr size_t smem = ST_ * (kBM + BN_) * kBK + kPromoWarps * (SW_ * 64) + 1024;   \
-        auto kernel = blockwise_gemm_kernel<BN_, ST_, PR_, PIPE_, SPLIT_, SW_>;              \
-        if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                        \
-        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, mo, p);                         \
+#define GI8_LAUNCH_BW(BN_, ST_, SPLIT_, NISS_, SLOT_)                                 \
+    do {                                                                              \
+        constexpr size_t smem = blockwise_smem_bytes(BN_, ST_);                       \
+        auto kernel = blockwise_gemm_kernel<BN_, ST_, SPLIT_, NISS_>;                 \
+        if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                 \
+        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, mo, p);                  \
     } while (0)
-    if (promo < PROMO_MAGIC || promo > PROMO_BIAS_X2) promo = PROMO_BIAS_X2;
-#ifndef GI8_ENABLE_ABLATIONS
-    if (promo > PROMO_I2F && promo != PROMO_BIAS_X2) promo = PROMO_BIAS_X2;  // ablation kernels: tuning builds only
-#endif
-    if (wide) {
-        GI8_LAUNCH_BWS(256, 3, PROMO_BIAS_X2, PIPE_X16_SINGLE, 2, 64, 52);
-    } else if (bn == 256) {
-        if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC, 13);
-        else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(256, 4, PROMO_MAGIC_X2, 14);
-#ifdef GI8_ENABLE_ABLATIONS
-        else if (promo == PROMO_ABLATE_HANDSHAKE) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_HANDSHAKE, 15);
-        else if (promo == PROMO_ABLATE_LOAD) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_LOAD, 16);
-        else if (promo == PROMO_ABLATE_SCALES) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_SCALES, 11);
-        else if (promo == PROMO_ABLATE_MATH) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_MATH, 12);
-        else if (promo == PROMO_ABLATE_FMA_ONLY) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_FMA_ONLY, 9);
-        else if (promo == PROMO_ABLATE_CVT_ONLY) GI8_LAUNCH_BW(256, 4, PROMO_ABLATE_CVT_ONLY, 10);
-#endif
-        else if (promo == PROMO_I2F && pipe == PIPE_X32_SINGLE && split == 2) GI8_LAUNCH_BWP(256, 4, PROMO_I2F, PIPE_X32_SINGLE, 2, 35);
-        else if (promo == PROMO_I2F && pipe == PIPE_X32_SINGLE) GI8_LAUNCH_BWP(256, 4, PROMO_I2F, PIPE_X32_SINGLE, 1, 32);
-        else if (promo == PROMO_I2F) GI8_LAUNCH_BW(256, 4, PROMO_I2F, 17);
-        else if (split == 2) GI8_LAUNCH_BWP(256, 4, PROMO_BIAS_X2, PIPE_X16_SINGLE, 2, 38);
-        else GI8_LAUNCH_BWP(256, 4, PROMO_BIAS_X2, PIPE_X16_SINGLE, 1, 39);
-    } else if (bn == 64) {
-        // Narrow tile for few-row problems: always the biased accumulator, one 16-column load per K block.
-        GI8_LAUNCH_BWP(64, 8, PROMO_BIAS_X2, PIPE_X16_SINGLE, 1, 41);
+    const bool two = knobs().bw_issuers == 2;
+    if (bn == 256) {
+        if (knobs().bw_halves == 2) {
+            if (two) GI8_LAUNCH_BW(256, 4, 2, 2, 13);
+            else GI8_LAUNCH_BW(256, 4, 2, 1, 14);
+        } else {
+            if (two) GI8_LAUNCH_BW(256, 4, 1, 2, 15);
+            else GI8_LAUNCH_BW(256, 4, 1, 1, 16);
+        }
+    } else if (bn == 128) {
+        if (two) GI8_LAUNCH_BW(128, 6, 1, 2, 17);
+        else GI8_LAUNCH_BW(128, 6, 1, 1, 18);
     } else {
-        if (promo == PROMO_MAGIC) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC, 18);
-        else if (promo == PROMO_MAGIC_X2) GI8_LAUNCH_BW(128, 6, PROMO_MAGIC_X2, 19);
-#ifdef GI8_ENABLE_ABLATIONS
-        else if (promo == PROMO_ABLATE_HANDSHAKE) GI8_LAUNCH_BW(128, 6, PROMO_ABLATE_HANDSHAKE, 20);
-        else if (promo == PROMO_ABLATE_LOAD) GI8_LAUNCH_BW(128, 6, PROMO_ABLATE_LOAD, 21);
-#endif
-        else if (promo == PROMO_I2F && pipe == PIPE_X32_SINGLE) GI8_LAUNCH_BWP(128, 6, PROMO_I2F, PIPE_X32_SINGLE, 1, 33);
-        else if (promo == PROMO_I2F) GI8_LAUNCH_BW(128, 6, PROMO_I2F, 22);
-        else GI8_LAUNCH_BWP(128, 6, PROMO_BIAS_X2, PIPE_X32_SINGLE, 1, 40);
+        if (two) GI8_LAUNCH_BW(64, 8, 1, 2, 19);
+        else GI8_LAUNCH_BW(64, 8, 1, 1, 20);
     }
 #undef GI8_LAUNCH_BW
-#undef GI8_LAUNCH_BWP
-#undef GI8_LAUNCH_BWS
     GI8_CUDA(cudaGetLastError());
     return GI8_OK;
 }

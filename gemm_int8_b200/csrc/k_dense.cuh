@@ -60,7 +60,8 @@ GI8_DEVICE void raise_error(uint32_t* status, volatile uint32_t* abort_flag, uin
 }
 
 // Bounded wait that also gives up when another role of this CTA has aborted.
-GI8_DEVICE bool wait_or_abort_addr(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag)
+GI8_DEVICE bool wait_or_abort_addr(uint32_t bar_addr, uint32_t parity, volatile uint32_t* abort_flag,
+                                   uint64_t limit_ns = GI8_WAIT_LIMIT_NS)
 {
     if (mbar_try_wait_addr(bar_addr, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
@@ -69,14 +70,15 @@ GI8_DEVICE bool wait_or_abort_addr(uint32_t bar_addr, uint32_t parity, volatile 
         if (mbar_try_wait_addr(bar_addr, parity)) return true;
         if ((++spins & 0x3f) == 0) {
             if (*abort_flag) return false;
-            if (globaltimer_ns() - t0 > GI8_WAIT_LIMIT_NS) return false;
+            if (globaltimer_ns() - t0 > limit_ns) return false;
         }
     }
 }
 
-GI8_DEVICE bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag)
+GI8_DEVICE bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
+                              uint64_t limit_ns = GI8_WAIT_LIMIT_NS)
 {
-    return wait_or_abort_addr(smem_u32(bar), parity, abort_flag);
+    return wait_or_abort_addr(smem_u32(bar), parity, abort_flag, limit_ns);
 }
 
 // Maps a linear tile index to (m block, n block).  Tiles are walked in bands of kGroupM row-blocks so

@@ -115,13 +115,17 @@ int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, 
 /*
  * N-sharded form of gi8_matmul_blockwise with the all-gather fused into the epilogue (no reference counterpart; the
  * reference is single-GPU).  This rank holds rows [col0, col0 + N) of the weight (y [N,K], sw [ceil(N/128), ...]) and
- * computes columns [col0, col0 + N) of the full [M, n_total] result; every 32 x 32 output block is written by TMA
- * store into ALL `n_outs` matrices `outs[i]` (bf16 [M, n_total], row-major, 16-byte aligned): this rank's own and
- * every peer's, the peers' through pointers that map their memory into this process (gi8_peer_import, or any other
- * peer mapping the host already has).  The transfer over NVLink overlaps the GEMM tile by tile; there is no separate
- * collective and no permuting copy.  After the call has completed on every rank (a barrier the host provides), every
- * matrix holds the full result.  col0 and N must be multiples of 32 (N may be ragged only at the end of n_total),
- * n_total a multiple of 8, n_outs <= 8.  Plain unicast stores only (no multicast).
+ * computes columns [col0, col0 + N) of the full [M, n_total] result; every output block (32 rows x 64 columns, or
+ * 32 x 32, see below) is written by TMA store into ALL `n_outs` matrices `outs[i]` (bf16 [M, n_total], row-major,
+ * 16-byte aligned): this rank's own and every peer's, the peers' through pointers that map their memory into this
+ * process (gi8_peer_import, or any other peer mapping the host already has).  The transfer over NVLink overlaps the
+ * GEMM tile by tile; there is no separate collective and no permuting copy.  After the call has completed on every
+ * rank (a barrier the host provides), every matrix holds the full result.  col0 and N must be multiples of 32 (N may
+ * be ragged only at the end of n_total), n_total a multiple of 8, n_outs <= 8.  Slices whose start and end are
+ * multiples of 64 (or end at n_total) use the wide tiles and 128-byte store rows, which is what NVLink wants; other
+ * slices take a 64-wide tile with 32 x 32 boxes so that no store reaches into a neighbour's columns.  A matrix may be
+ * overwritten by a peer as soon as that peer starts its next call: the host must not start call i + 1 on any rank
+ * before every rank has finished reading the result of call i.  Plain unicast stores only (no multicast).
  */
 int gi8_matmul_blockwise_allgather(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
                                    int64_t ld_sw, void* const* outs, int n_outs, int64_t M, int64_t N, int64_t K,
@@ -165,11 +169,10 @@ int gi8_hadamard_quantize_token_block(const void* in, int in_dtype, int8_t* q, f
 /*
  * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted
  * per-shape dispatch that replaces the reference's shape table (csrc/kernels/gemm.cu:136-161).
- * Names: "dense_bn256", "dense_bn128", "dense_bn64", "smallm" (split-K through global scratch),
- * "smallm_cluster" (split-K through distributed shared memory), "gemv" (weight-streaming dp4a kernel for
- * M <= 8 of the scaled entry point), "pair" (two-CTA tiles with
- * tcgen05.mma.cta_group::2: 256 x 256 for the dense entry points, 256 x 128 for the blockwise one), "auto".  Returns GI8_ERR_INVALID_ARGUMENT
- * for an unknown name.
+ * Names: "dense_bn256", "dense_bn128", "dense_bn64" (tile width of the dense and of the blockwise kernel), "smallm"
+ * (split-K through global scratch), "smallm_cluster" (split-K through distributed shared memory), "pair" (dense
+ * entry points only: 256 x 256 two-CTA tiles with tcgen05.mma.cta_group::2), "auto".  Returns
+ * GI8_ERR_INVALID_ARGUMENT for an unknown name.
  */
 int gi8_force_variant(const char* name);
 
@@ -182,6 +185,27 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K);
  * (low byte: 1 producer, 2 MMA, 3 epilogue, 4 drain, 5 reduce wait expired; upper bits: CTA index).
  */
 int gi8_device_status(uint32_t* code);
+
+/*
+ * gi8_device_status as a status code: GI8_OK, or GI8_ERR_DEVICE_TIMEOUT (with the role and CTA in gi8_last_error) when
+ * a kernel since the last check gave up one of its bounded waits -- the counterpart of the exceptions the reference
+ * throws on a failed launch (csrc/kernels/gemm.cu:108-121).  SYNCHRONISES the device and clears the word.
+ */
+int gi8_device_check(void);
+
+/*
+ * Launches a one-CTA kernel whose only job is to let a bounded wait run out (a 1 ms wait on a barrier nobody arrives
+ * on), so that hosts and tests can see the whole error path -- status word, gi8_device_check, a context that stays
+ * usable -- without a faulting or hanging kernel.  No reference counterpart.
+ */
+int gi8_selftest_wait_timeout(void* stream);
+
+/*
+ * The GEMM_INT8_* tuning variables (tile band height, TMA-store epilogue, programmatic dependent launch, K splits,
+ * blockwise MMA shape and issuer count) are read once, when the library is first used; this reads them again.
+ * No reference counterpart (its tuning is compile-time, CMakeLists.txt:49-51).
+ */
+int gi8_reload_env(void);
 
 #ifdef __cplusplus
 }

@@ -158,7 +158,7 @@ def test_reference_benchmark_shapes(g, oracle):
 
 
 # ---------------------------------------------------------------------------------------- scaled (per token x per channel)
-@pytest.mark.parametrize("variant", DENSE_VARIANTS + ["smallm", "smallm_cluster", "gemv", None])
+@pytest.mark.parametrize("variant", DENSE_VARIANTS + ["smallm", "smallm_cluster", None])
 def test_scaled_edge_shapes(g, oracle, variant):
     g.force_variant(variant)
     gen = torch.Generator().manual_seed(41)
@@ -178,10 +178,10 @@ def test_config3_decode_shapes(g, oracle, K, N):
 
     for M in (1, 4, 16, 64):
         xq, wq, sx, sw = workloads.decode(M, N, K)
-        assert g.pick_variant(1, M, N, K) in ("smallm_cluster", "gemv")
+        assert g.pick_variant(1, M, N, K) == "smallm_cluster"
         ref = oracle.c_matmul_scaled(xq, wq, sx, sw)
-        # the automatic choice, the cluster reduction, the global-scratch reduction and the streaming kernel
-        for variant in (None, "smallm_cluster", "smallm", "gemv"):
+        # the automatic choice, the cluster reduction and the global-scratch reduction
+        for variant in (None, "smallm_cluster", "smallm"):
             g.force_variant(variant)
             out = g.matmul_scaled(xq.cuda(), wq.cuda(), sx.cuda(), sw.cuda())
             assert_bits_equal(oracle, out, ref, f"decode {variant} M={M} N={N} K={K}")
@@ -223,8 +223,23 @@ def test_smallm_split_k_scratch_is_left_zeroed(g, oracle):
 
 
 # ---------------------------------------------------------------------------------------- blockwise
-@pytest.mark.parametrize("variant", ["dense_bn64", "dense_bn128", "dense_bn256", "pair", None])
-def test_blockwise_edge_shapes(g, oracle, variant):
+@pytest.fixture
+def bw_knobs(g, monkeypatch):
+    """Sets the blockwise kernel's tuning variables for one test and restores the defaults afterwards."""
+    def set_knobs(halves, issuers):
+        monkeypatch.setenv("GEMM_INT8_BW_HALVES", str(halves))
+        monkeypatch.setenv("GEMM_INT8_BW_ISSUERS", str(issuers))
+        g.reload_env()
+    yield set_knobs
+    monkeypatch.delenv("GEMM_INT8_BW_HALVES", raising=False)
+    monkeypatch.delenv("GEMM_INT8_BW_ISSUERS", raising=False)
+    g.reload_env()
+
+
+@pytest.mark.parametrize("issuers", [1, 2])
+@pytest.mark.parametrize("variant", ["dense_bn64", "dense_bn128", "dense_bn256", None])
+def test_blockwise_edge_shapes(g, oracle, variant, issuers, bw_knobs):
+    bw_knobs(1, issuers)
     g.force_variant(variant)
     gen = torch.Generator().manual_seed(51)
     shapes = [(1, 8, 16), (7, 120, 128), (33, 136, 144), (128, 128, 128), (129, 264, 400), (257, 1000, 1040),
@@ -241,24 +256,24 @@ def test_blockwise_edge_shapes(g, oracle, variant):
     g.force_variant(None)
 
 
-@pytest.mark.parametrize("halves", ["1", "2"])
-@pytest.mark.parametrize("promotion", ["0", "1", "2", "9"])
-def test_blockwise_promotion_modes_agree(g, oracle, promotion, halves, monkeypatch):
-    """The promotion arithmetics (scalar magic-number, packed, cvt + fma, biased accumulator) and the two MMA
-    shapes of the 256-wide tile are bit-identical."""
-    monkeypatch.setenv("GEMM_INT8_PROMOTION", promotion)
-    monkeypatch.setenv("GEMM_INT8_HALVES", halves)
+@pytest.mark.parametrize("halves", [1, 2])
+@pytest.mark.parametrize("issuers", [1, 2])
+def test_blockwise_mma_forms_agree(g, oracle, halves, issuers, bw_knobs):
+    """The MMA shapes of the 256-wide tile (N = 256, or two column halves with N = 128) and one or two issuing
+    threads give the oracle's bits, including the largest possible block partial and many K blocks per tile
+    (the barrier rings wrap many times)."""
+    bw_knobs(halves, issuers)
     gen = torch.Generator().manual_seed(52)
-    for variant in ("dense_bn128", "dense_bn256", "pair"):
+    for variant in ("dense_bn64", "dense_bn128", "dense_bn256"):
         g.force_variant(variant)
-        for (M, N, K) in [(130, 264, 400), (300, 1000, 2048)]:
+        for (M, N, K) in [(130, 264, 400), (300, 1000, 2048), (140, 520, 8192)]:
             KB, NB = -(-K // 128), -(-N // 128)
             x, y = rand_i8((M, K), M + 3), rand_i8((N, K), N + 3)
             x[0], y[0] = -128, -128          # largest possible block partial, 2^21
             sa = torch.rand(M, KB, generator=gen) * 0.02 + 1e-3
             sw = torch.rand(NB, KB, generator=gen) * 0.02 + 1e-3
             out = g.matmul_blockwise(x.cuda(), y.cuda(), sa.cuda(), sw.cuda())
-            assert_bits_equal(oracle, out, oracle.c_matmul_blockwise(x, y, sa, sw), f"promotion {promotion} {variant}")
+            assert_bits_equal(oracle, out, oracle.c_matmul_blockwise(x, y, sa, sw), f"halves {halves} issuers {issuers} {variant}")
     g.force_variant(None)
 
 
