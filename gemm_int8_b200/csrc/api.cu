@@ -56,15 +56,15 @@ std::atomic<int> g_forced_variant{VAR_AUTO};
 //   GEMM_INT8_TMA_STORE  = 0       bf16 epilogues store from registers instead of through shared memory + TMA
 //   GEMM_INT8_PDL        = 0       small-M kernels are launched without programmatic dependent launch
 //   GEMM_INT8_SPLITS     = n       small-M kernels: number of K splits
-//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256, or two column halves with N = 128
-//   GEMM_INT8_BW_ISSUERS = 1 | 2   blockwise kernel: MMA-issuing threads
+//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256, or (default) two column halves with N = 128
+//   GEMM_INT8_BW_ISSUERS = 1 | 2   blockwise kernel without column halves: MMA-issuing threads (default 2)
 struct Knobs {
     int group_m = 0;
     bool tma_store = true;
     bool pdl = true;
     int splits = 0;
-    int bw_halves = 1;
-    int bw_issuers = 1;
+    int bw_halves = 2;
+    int bw_issuers = 2;
 };
 Knobs g_knobs;
 std::once_flag g_knobs_once;
@@ -79,8 +79,8 @@ void load_knobs()
     if (const char* e = getenv("GEMM_INT8_TMA_STORE")) k.tma_store = e[0] != '0';
     if (const char* e = getenv("GEMM_INT8_PDL")) k.pdl = e[0] != '0';
     if (const char* e = getenv("GEMM_INT8_SPLITS")) k.splits = atoi(e);
-    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 2 ? 2 : 1;
-    if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 2 ? 2 : 1;
+    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 1 ? 1 : 2;
+    if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 1 ? 1 : 2;
     g_knobs = k;
 }
 
@@ -227,8 +227,9 @@ int check_common(const void* x, const void* y, const void* out, int64_t M, int64
 // measured inefficiency of the narrower tensor-core instruction (its shared-memory operand traffic per MAC is
 // higher): dense 2900 / 1750 / 1000 TOP/s and blockwise 1900 / 1520 / 850 TOP/s at BN = 256 / 128 / 64.
 // ---------------------------------------------------------------------------------------------------
-int pick_bn(int64_t M, int64_t N, int sms, bool blockwise)
+int pick_bn(int64_t M, int64_t N, int sms, bool blockwise, bool* pair = nullptr)
 {
+    if (pair) *pair = false;
     const int cand[3] = {256, 128, 64};
     const double ineff_dense[3] = {1.0, 1.65, 2.9};
     const double ineff_block[3] = {1.0, 1.35, 2.4};
@@ -852,28 +853,34 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
     p.n_out = 1, p.out_col0 = 0;
+    const int forced = g_forced_variant;
     int bn;
-    switch (static_cast<int>(g_forced_variant)) {  // (the two-CTA variant exists for the dense kernel only)
+    bool pair = false;
+    switch (forced) {
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
         case VAR_DENSE_BN64: bn = 64; break;
-        default: bn = pick_bn(M, N, st->sm_count, true);
+        case VAR_PAIR: bn = 256, pair = true; break;
+        default: bn = pick_bn(M, N, st->sm_count, true, &pair);
     }
     // The epilogue's TMA-store boxes are 64 columns wide for the 256- and 128-wide tiles and 32 for the 64-wide one.
     // A box is clipped at the edge of the tensor map, i.e. of the whole [M, n_total] matrix, not at the edge of this
     // GEMM's column slice: a slice that starts or ends inside a box (and is not the last one) would overwrite its
     // neighbour's columns, so such slices take the narrow tile, whose boxes the slice contract (multiples of 32)
     // always fits.
-    if (gather && (col0 % 64 != 0 || (N % 64 != 0 && col0 + N != n_total))) bn = 64;
+    if (gather && (col0 % 64 != 0 || (N % 64 != 0 && col0 + N != n_total))) bn = 64, pair = false;
     const int box_cols = blockwise_store_cols(bn);
     CUtensorMap mx, my;
     if (int rc = make_operand_map(&mx, x, M, K, kBM)) return rc;
-    if (int rc = make_operand_map(&my, y, N, K, bn)) return rc;
-    p.tiles_m = (int)((M + kBM - 1) / kBM);
+    if (int rc = make_operand_map(&my, y, N, K, pair ? bn / 2 : bn)) return rc;
+    const int tile_m = pair ? 2 * kBM : kBM;
+    p.tiles_m = (int)((M + tile_m - 1) / tile_m);
     p.tiles_n = (int)((N + bn - 1) / bn);
     p.group_m = pick_group_m(p.K);
+    if (pair) p.group_m = p.group_m / 2 > 0 ? p.group_m / 2 : 1;
     const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
-    const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
+    const int slots = pair ? st->sm_count / 2 : st->sm_count;
+    const int grid = static_cast<int>(tiles < slots ? tiles : slots) * (pair ? 2 : 1);
     OutputMaps mo{};
     if (gather) {
         for (int i = 0; i < n_out; ++i)
@@ -884,31 +891,43 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         if (p.tma_store)
             if (int rc = make_output_map(&mo.m[0], out, M, N, N, box_cols)) return rc;
     }
-#define GI8_LAUNCH_BW(BN_, ST_, SPLIT_, NISS_, SLOT_)                                 \
-    do {                                                                              \
-        constexpr size_t smem = blockwise_smem_bytes(BN_, ST_);                       \
-        auto kernel = blockwise_gemm_kernel<BN_, ST_, SPLIT_, NISS_>;                 \
-        if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                 \
-        kernel<<<grid, kBlockwiseThreads, smem, s>>>(mx, my, mo, p);                  \
+#define GI8_LAUNCH_BW(BN_, ST_, SPLIT_, NISS_, PAIR_, SLOT_)                                  \
+    do {                                                                                      \
+        constexpr size_t smem = blockwise_smem_bytes(BN_, ST_, PAIR_);                        \
+        auto kernel = blockwise_gemm_kernel<BN_, ST_, SPLIT_, NISS_, PAIR_>;                  \
+        if (int rc = ensure_smem(st, SLOT_, kernel, smem)) return rc;                         \
+        cudaLaunchConfig_t cfg{};                                                             \
+        cfg.gridDim = dim3(grid, 1, 1);                                                       \
+        cfg.blockDim = dim3(kBlockwiseThreads, 1, 1);                                         \
+        cfg.dynamicSmemBytes = smem;                                                          \
+        cfg.stream = s;                                                                       \
+        cudaLaunchAttribute attr[1];                                                          \
+        attr[0].id = cudaLaunchAttributeClusterDimension;                                     \
+        attr[0].val.clusterDim.x = PAIR_ ? 2 : 1;                                             \
+        attr[0].val.clusterDim.y = 1;                                                         \
+        attr[0].val.clusterDim.z = 1;                                                         \
+        cfg.attrs = attr;                                                                     \
+        cfg.numAttrs = 1;                                                                     \
+        GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mx, my, mo, p));                            \
     } while (0)
     const bool two = knobs().bw_issuers == 2;
-    if (bn == 256) {
-        if (knobs().bw_halves == 2) {
-            if (two) GI8_LAUNCH_BW(256, 4, 2, 2, 13);
-            else GI8_LAUNCH_BW(256, 4, 2, 1, 14);
-        } else {
-            if (two) GI8_LAUNCH_BW(256, 4, 1, 2, 15);
-            else GI8_LAUNCH_BW(256, 4, 1, 1, 16);
-        }
+    const bool halves = knobs().bw_halves == 2;
+    if (pair) {
+        if (halves) GI8_LAUNCH_BW(256, 6, 2, 2, true, 21);
+        else if (two) GI8_LAUNCH_BW(256, 6, 1, 2, true, 22);
+        else GI8_LAUNCH_BW(256, 6, 1, 1, true, 23);
+    } else if (bn == 256) {
+        if (halves) GI8_LAUNCH_BW(256, 4, 2, 2, false, 13);
+        else if (two) GI8_LAUNCH_BW(256, 4, 1, 2, false, 15);
+        else GI8_LAUNCH_BW(256, 4, 1, 1, false, 16);
     } else if (bn == 128) {
-        if (two) GI8_LAUNCH_BW(128, 6, 1, 2, 17);
-        else GI8_LAUNCH_BW(128, 6, 1, 1, 18);
+        if (two) GI8_LAUNCH_BW(128, 6, 1, 2, false, 17);
+        else GI8_LAUNCH_BW(128, 6, 1, 1, false, 18);
     } else {
-        if (two) GI8_LAUNCH_BW(64, 8, 1, 2, 19);
-        else GI8_LAUNCH_BW(64, 8, 1, 1, 20);
+        if (two) GI8_LAUNCH_BW(64, 8, 1, 2, false, 19);
+        else GI8_LAUNCH_BW(64, 8, 1, 1, false, 20);
     }
 #undef GI8_LAUNCH_BW
-    GI8_CUDA(cudaGetLastError());
     return GI8_OK;
 }
 

@@ -10,12 +10,13 @@
 //               (or 2 x 4 with N = 128 when SPLIT == 2) that overwrite one of NBUF = 512 / BN tensor-memory partial
 //               buffers, then ONE commit per column half that both frees the pipeline stage and publishes the
 //               partial; warp 2 allocates tensor memory.
-//   warps 4..11 promotion (setmaxnreg.inc): warp w owns TMEM lane quarter (w % 4) and column half ((w - 4) / 4) of
-//               the tile, i.e. 32 rows x BN/2 columns, whose fp32 accumulators it keeps in registers (as f32x2
-//               pairs).  Per K block: tcgen05.ld the int32 partial in 32-column chunks, hand the buffer back after
-//               the last load, cvt.rn.f32.s32 + fma.rn.f32x2 with the block's scale.  A column half never
-//               straddles a 128-wide weight-scale block.  At the end of the tile the same warps cast to bf16 and
-//               store through swizzled shared memory and TMA.
+//   warps 4..11 promotion (setmaxnreg.inc): warp w owns TMEM lane quarter (w % 4) and BN/2 of the tile's columns
+//               (with column halves: 64 columns of each half), i.e. 32 rows x BN/2 columns, whose fp32
+//               accumulators it keeps in registers (as f32x2 pairs).  Per K block and half: tcgen05.ld the int32
+//               partial in 32-column chunks, hand the half back after the last load, cvt.rn.f32.s32 +
+//               fma.rn.f32x2 with the block's scale.  A warp's segment never straddles a 128-wide weight-scale
+//               block.  At the end of the tile the same warps cast to bf16 and store through swizzled shared
+//               memory and TMA.
 //
 // Why eight fat warps (measured on B200 with a stand-alone loop of the same instructions, cycles per 128 x 256
 // K block, tensor core busy in the background): a tcgen05.ld costs about one cycle per 32-lane column whatever its
@@ -27,18 +28,19 @@
 // Barrier protocol (every wait is a parity wait, so it must hold that a barrier cannot complete a second phase
 // before the waiter has consumed the first; the comment at each barrier says what gates its next phase):
 //   bar_full[s]        completed by the TMA bytes of K block `it` (s = it % STAGES).  Waiter: the issuer of K block
-//                      `it`.  Next phase needs the producer to refill stage s, which needs bar_done[.][s] of K block
-//                      `it`, which needs this issuer's commit: gated by the waiter.
+//                      `it` (with column halves: both issuers, each of which visits every K block).  Next phase
+//                      needs the producer to refill stage s, which needs bar_done[h][s] of K block `it` for every
+//                      half h, i.e. every waiting issuer's own commit: gated by each waiter.
 //   bar_done[h][s]     completed by the issuer's commit for column half h of K block `it`.  Waiters: the producer
-//                      (before refilling s; the next completion needs its own refill: gated) and the promotion warps
-//                      of half h (the next completion is K block it + STAGES, whose MMAs need partial buffer
-//                      (it + STAGES) % NBUF handed back by every warp of the half for K block it + STAGES - NBUF >= it:
-//                      gated).
-//   bar_part_empty[h][b]  completed by the arrivals of the promotion warps of half h after their last load of a
-//                      K block in buffer b.  Waiter: the issuer of the next K block that uses b; the completion
-//                      after that needs this issuer's MMAs: gated.
-//   With two issuers, issuer j takes K blocks it % 2 == j, hence stages s % 2 == j and buffers b % 2 == j
-//   (STAGES and NBUF are even): every barrier still has exactly one issuing waiter, which sees all its phases.
+//                      (before refilling s; the next completion needs its own refill: gated) and all promotion
+//                      warps (the next completion is K block it + STAGES, whose MMAs need half h of partial buffer
+//                      (it + STAGES) % NBUF handed back by every warp for K block it + STAGES - NBUF >= it: gated).
+//   bar_part_empty[h][b]  completed by the arrivals of all eight promotion warps after their last load of half h of
+//                      a K block in buffer b.  Waiter: the issuer of half h of the next K block that uses b; the
+//                      completion after that needs this issuer's MMAs: gated.
+//   Without column halves and with two issuers, issuer j takes K blocks it % 2 == j, hence stages s % 2 == j and
+//   buffers b % 2 == j (STAGES and NBUF are even): every barrier still has exactly one issuing waiter, which sees
+//   all its phases.
 #pragma once
 
 #include "k_dense.cuh"
@@ -78,9 +80,9 @@ struct OutputMaps {
 // Columns of one TMA-store box of the epilogue for a tile BN wide: 64 (32 rows x 128 bytes, 128-byte swizzle) when
 // a promotion warp owns at least 64 columns, else 32 (32 rows x 64 bytes, 64-byte swizzle).
 __host__ __device__ constexpr int blockwise_store_cols(int bn) { return bn / 2 >= 64 ? 64 : 32; }
-__host__ __device__ constexpr size_t blockwise_smem_bytes(int bn, int stages)
+__host__ __device__ constexpr size_t blockwise_smem_bytes(int bn, int stages, bool pair = false)
 {
-    return static_cast<size_t>(stages) * (kBM + bn) * kBK + kPromoWarps * blockwise_store_cols(bn) * 64 + 1024;
+    return static_cast<size_t>(stages) * (kBM + (pair ? bn / 2 : bn)) * kBK + kPromoWarps * blockwise_store_cols(bn) * 64 + 1024;
 }
 
 template <int N>
@@ -119,6 +121,17 @@ GI8_DEVICE uint64_t splat_f32x2(float t)
     return r;
 }
 
+// a * b (fp32, round to nearest) as a volatile statement: it keeps its place among the other volatile statements
+// (tensor-memory loads, conversions).  The scales are loaded two K blocks before their use; written as plain C++ the
+// compiler hoists the product up to the loads to save a register, and the warp then waits out the L2 latency right
+// there (measured: 150 cycles per K block).
+GI8_DEVICE float mul_in_place(float a, float b)
+{
+    float r;
+    asm volatile("mul.rn.f32 %0, %1, %2;" : "=f"(r) : "f"(a), "f"(b));
+    return r;
+}
+
 GI8_DEVICE void unpack_f32x2(uint64_t v, float& lo, float& hi)
 {
     asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
@@ -136,10 +149,27 @@ GI8_DEVICE uint32_t pack_bf16x2_of(uint64_t pair)
 // recomputing the value.
 #define GI8_PIN(v) asm volatile("" : "+r"(v))
 
-// SPLIT = 2 (BN = 256 only): the MMAs of a K block are issued as two column halves (N = 128 each), each half with
-// its own commit and its own hand-back barrier, so the four promotion warps of the first half start half an MMA
-// time earlier.  NISS: number of MMA-issuing threads (1 or 2, alternate K blocks).
-template <int BN, int STAGES, int SPLIT, int NISS>
+// SPLIT = 2 (BN = 256 only): the MMAs of a K block are issued as two column halves (N = 128 each), each half by its
+// own issuing thread, with its own commit and its own hand-back barrier, and EVERY promotion warp takes 64 columns of
+// each half.  A half's partial buffer is then held for two loads and one chunk of arithmetic instead of four and
+// three, and the tensor core refills one half while the warps read the other: with only two 256-column buffers in
+// tensor memory the time a buffer is held, plus the latencies of the two hand-overs, is what bounds the K-block
+// period (measured: 1000-1200 cycles per K block with contiguous 128-column ownership, where neither instruction
+// issue (51 %) nor any pipe was saturated).
+// SPLIT = 1: MMAs with N = BN; NISS issuing threads (1 or 2) take alternate K blocks.
+// PAIR: two CTAs on neighbouring SMs (a 2 x 1 x 1 cluster) share one 256 x BN tile, as in the dense kernel: the
+// leader's issuers run tcgen05.mma.cta_group::2 (M = 256), each CTA loads its own 128 rows of x and HALF of the BN
+// rows of y, keeps the partials of its 128 rows in its own tensor memory and promotes them with its own eight warps.
+// Per SM that is a third fewer operand bytes per K block (32 KB instead of 48 KB, so six pipeline stages instead of
+// four fit) and half the MMA instructions.  It matters because the 1-CTA kernel is bound by bytes in flight: with four
+// 48 KB stages, one of them being read by the tensor core, 144 KB are in flight against an L2 latency of about 2000
+// cycles under load -- 72 bytes per cycle, i.e. 670 cycles per 48 KB K block where the tensor core needs 512.  TMA
+// loads are unicast into the issuing CTA's shared memory and signal the leader's barrier; the commits are two
+// unicast tcgen05.commit (no multicast anywhere).
+// An N = 128 two-CTA MMA (column halves) takes 64 rows of y from each CTA, so half h of the partial holds tile
+// columns [64 h, 64 h + 64) and [128 + 64 h, 128 + 64 h + 64): a promotion warp's 64-column segment of half h is then
+// tile columns cg * 128 + h * 64 .. (still contiguous and inside one weight-scale block).
+template <int BN, int STAGES, int SPLIT, int NISS, bool PAIR = false>
 __global__ void __launch_bounds__(kBlockwiseThreads, 1)
 blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                       const __grid_constant__ OutputMaps outs, const BlockwiseParams p)
@@ -147,22 +177,31 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     static_assert(BN == 64 || BN == 128 || BN == 256, "BN must be 64, 128 or 256");
     static_assert(SPLIT == 1 || (SPLIT == 2 && BN == 256), "column halves only for the 256-wide tile");
     static_assert(NISS == 1 || NISS == 2, "one or two MMA issuers");
-    constexpr int NBUF = 512 / BN;    // partial buffers in tensor memory (2, 4 or 8)
-    constexpr int NSUB = BN / SPLIT;  // N of one MMA
-    constexpr int CW = BN / 2;        // columns per promotion warp (128, 64 or 32)
-    constexpr int NC = CW / 32;       // 32-column loads per K block and warp
+    static_assert(SPLIT == 1 || NISS == 2, "with column halves there is one issuer per half");
+    constexpr int NBUF = 512 / BN;       // partial buffers in tensor memory (2, 4 or 8)
+    constexpr int NSUB = BN / SPLIT;     // N of one MMA = columns of one half
+    constexpr int CW = BN / 2;           // columns per promotion warp (128, 64 or 32) ...
+    constexpr int SEGW = CW / SPLIT;     // ... as SPLIT segments of SEGW columns, one in each half
+    constexpr int NC = SEGW / 32;        // 32-column loads per segment
     constexpr int STORE_W = blockwise_store_cols(BN);
-    // Each issuer must own the stages and the partial buffers of its K blocks (see the protocol above): with an odd
-    // count an issuer would meet a barrier only every second phase, which a parity wait cannot tell apart.
-    static_assert(STAGES % NISS == 0 && NBUF % NISS == 0, "issuers must own their stages and partial buffers");
+    static_assert(SEGW % STORE_W == 0 && SEGW % 32 == 0, "segments are whole store boxes and whole loads");
+    // SPLIT == 1: each issuer must own the stages and the partial buffers of its K blocks (see the protocol above):
+    // with an odd count an issuer would meet a barrier only every second phase, which a parity wait cannot tell apart.
+    static_assert(SPLIT == 2 || (STAGES % NISS == 0 && NBUF % NISS == 0), "issuers must own their stages and partial buffers");
     // A promotion warp's parity wait on bar_done is safe only if the commit STAGES K blocks later needs a partial
     // buffer that the same warp hands back after the awaited K block (see the protocol above).
     static_assert(STAGES >= NBUF, "the stage ring must be at least as deep as the partial-buffer ring");
+    static_assert(!PAIR || BN == 256, "two-CTA tiles are 256 wide");
+    constexpr int kTileM = PAIR ? 2 * kBM : kBM;  // rows of the (pair's) tile
+    constexpr int kRowsB = PAIR ? BN / 2 : BN;    // rows of y this CTA loads
     constexpr uint32_t kBytesA = kBM * kBK;
-    constexpr uint32_t kBytesB = BN * kBK;
+    constexpr uint32_t kBytesB = kRowsB * kBK;
     constexpr uint32_t kStageBytes = kBytesA + kBytesB;
     constexpr uint32_t kTmemCols = 512;
-    constexpr uint32_t kIdesc = make_idesc_i8(kBM, NSUB, false);
+    constexpr uint32_t kIdesc = make_idesc_i8(kTileM, NSUB, false);
+    // Tile column of the first column of segment (half h, column group cg), see above.
+    constexpr int kSegStrideH = (PAIR && SPLIT == 2) ? SEGW : NSUB;
+    constexpr int kSegStrideCg = (PAIR && SPLIT == 2) ? NSUB : SEGW;
     constexpr uint32_t kStoreBytes = STORE_W * 64;  // one staging block per promotion warp: 32 rows x STORE_W bf16
 
     extern __shared__ uint8_t smem_raw[];
@@ -176,8 +215,12 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int num_tiles = p.tiles_m * p.tiles_n;
+    const int num_tiles = p.tiles_m * p.tiles_n;  // tiles_m counts kTileM-row tiles
     const int num_kb = (p.K + kBK - 1) / kBK;
+    // PAIR: rank 0 is the leader (its bar_full and bar_part_empty serve both CTAs); the pair is the scheduling unit.
+    const uint32_t rank = PAIR ? cluster_cta_rank() : 0u;
+    const int first_tile = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -186,18 +229,24 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             for (int h = 0; h < SPLIT; ++h) mbar_init(&bar_done[h][s], 1);
         }
         for (int b = 0; b < NBUF; ++b) {
-            for (int h = 0; h < SPLIT; ++h) mbar_init(&bar_part_empty[h][b], kPromoWarps / SPLIT);
+            for (int h = 0; h < SPLIT; ++h) mbar_init(&bar_part_empty[h][b], PAIR ? 2 * kPromoWarps : kPromoWarps);
         }
         fence_barrier_init();
         prefetch_tensormap(&map_x);
         prefetch_tensormap(&map_y);
     }
     if (warp == 2) {
-        tmem_alloc(&tmem_base_slot, kTmemCols);
-        tmem_relinquish_alloc_permit();
+        if constexpr (PAIR) {
+            tmem_alloc_pair(&tmem_base_slot, kTmemCols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(&tmem_base_slot, kTmemCols);
+            tmem_relinquish_alloc_permit();
+        }
     }
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // both CTAs' barriers exist before anything signals them remotely
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
@@ -214,7 +263,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             uint32_t s = 0, ph = 0;  // stage and phase parity of the running K-block counter
             uint32_t armed = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
                 int mb, nb;
                 tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
                 for (int kb = 0; kb < num_kb; ++kb) {
@@ -227,17 +276,27 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     }
                     if (elect_one()) {
                         uint8_t* sa_tile = smem + s * kStageBytes;
-                        mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
-                        tma_load_2d(sa_tile, &map_x, &bar_full[s], kb * kBK, mb * kBM);
-                        tma_load_2d(sa_tile + kBytesA, &map_y, &bar_full[s], kb * kBK, nb * BN);
+                        if constexpr (PAIR) {
+                            // The leader arms its barrier for the bytes of BOTH CTAs; the peer only sends bytes.
+                            const uint32_t leader_full = map_to_cta(smem_u32(&bar_full[s]), 0);
+                            if (rank == 0) mbar_arrive_expect_tx(&bar_full[s], 2 * kStageBytes);
+                            tma_load_2d_pair(sa_tile, &map_x, leader_full, kb * kBK, mb * kTileM + static_cast<int>(rank) * kBM);
+                            tma_load_2d_pair(sa_tile + kBytesA, &map_y, leader_full, kb * kBK, nb * BN + static_cast<int>(rank) * kRowsB);
+                        } else {
+                            mbar_arrive_expect_tx(&bar_full[s], kStageBytes);
+                            tma_load_2d(sa_tile, &map_x, &bar_full[s], kb * kBK, mb * kBM);
+                            tma_load_2d(sa_tile + kBytesA, &map_y, &bar_full[s], kb * kBK, nb * BN);
+                        }
                     }
                     __syncwarp();
                     if (armed < STAGES) ++armed;
                     if (++s == STAGES) s = 0, ph ^= 1;
                 }
             }
-            // Drain: every armed stage must have landed before the CTA may exit.  (s, ph) is the slot after the last
-            // armed one; walk backwards over the armed stages.
+            // Drain: every armed stage must have landed before the CTA may exit (PAIR: the leader's barriers complete
+            // only when both CTAs' bytes have landed; the peer leaves through the final cluster barrier).  (s, ph) is
+            // the slot after the last armed one; walk backwards over the armed stages.
+            if (PAIR && rank != 0) armed = 0;
             for (uint32_t j = 0; j < armed; ++j) {
                 if (s == 0) s = STAGES, ph ^= 1;
                 --s;
@@ -246,47 +305,55 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     break;
                 }
             }
-        } else if (warp == 1 || (NISS == 2 && warp == 3)) {
-            // -------------------------------------------------------------- MMA issuer(s)
-            const uint32_t first = (NISS == 2 && warp == 3) ? 1u : 0u;
+        } else if ((warp == 1 || (NISS == 2 && warp == 3)) && rank == 0) {
+            // -------------------------------------------------------------- MMA issuer(s) (PAIR: the leader's)
+            const uint32_t me = warp == 1 ? 0u : 1u;
+            // SPLIT == 2: issuer `me` issues column half `me` of EVERY K block.  SPLIT == 1: issuer `me` issues the
+            // K blocks with it % NISS == me.
+            constexpr uint32_t kStep = SPLIT == 2 ? 1u : static_cast<uint32_t>(NISS);
+            const uint32_t first = SPLIT == 2 ? 0u : me;
+            const uint32_t h = SPLIT == 2 ? me : 0u;
             int my_tiles = 0;
-            for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) ++my_tiles;
+            for (int tile = first_tile; tile < num_tiles; tile += tile_step) ++my_tiles;
             const uint32_t total = static_cast<uint32_t>(my_tiles) * static_cast<uint32_t>(num_kb);
-            // stage / partial buffer of K block `it` and their phase parities, stepped by NISS without divisions
+            // stage / partial buffer of K block `it` and their phase parities, stepped without divisions
             uint32_t s = first, ph = 0, buf = first, bph = 0;
-            for (uint32_t it = first; it < total; it += NISS) {
+            uint64_t* const done_h = &bar_done[h][0];
+            uint64_t* const empty_h = &bar_part_empty[h][0];
+            for (uint32_t it = first; it < total; it += kStep) {
                 // The operands first (they land long before the partial buffer is free), so that nothing but the
                 // MMAs stands between the buffer hand-back and the tensor core.
                 bool issued = wait_or_abort(&bar_full[s], ph, &abort_flag);
-                const uint32_t tmem_d = tmem_base + buf * BN;
+                // Half h: rows h * NSUB.. of the weight tile (PAIR: rows h * NSUB / 2.. of each CTA's half of it) into
+                // columns h * NSUB.. of the partial buffer.
+                const uint32_t tmem_d = tmem_base + buf * BN + h * NSUB;
                 const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
                 const uint64_t da = make_smem_desc_k128(a_addr);
-                const uint64_t db = make_smem_desc_k128(a_addr + kBytesA);
-#pragma unroll
-                for (int h = 0; h < SPLIT && issued; ++h) {
-                    if (!wait_or_abort(&bar_part_empty[h][buf], bph ^ 1, &abort_flag)) {
-                        issued = false;
-                        break;
-                    }
-                    tcgen05_fence_after_sync();
-                    if (elect_one()) {
-                        // Half h: rows h * NSUB.. of the weight tile (NSUB rows of 128 bytes: 16-byte units in
-                        // the descriptor's address field) into columns h * NSUB.. of the partial buffer.  The
-                        // first K step overwrites the buffer.
-#pragma unroll
-                        for (int k = 0; k < kBK / kUmmaK; ++k)
-                            umma_i8(tmem_d + h * NSUB, da + 2 * k, db + (h * NSUB * kBK) / 16 + 2 * k, kIdesc, k != 0 ? 1u : 0u);
-                        umma_commit(&bar_done[h][s]);
-                    }
-                    __syncwarp();
-                }
+                const uint64_t db = make_smem_desc_k128(a_addr + kBytesA + h * (PAIR ? NSUB / 2 : NSUB) * kBK);
+                issued = issued && wait_or_abort(&empty_h[buf], bph ^ 1, &abort_flag);
                 if (!issued) {
                     if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
                     break;
                 }
-                s += NISS;
+                tcgen05_fence_after_sync();
+                if (elect_one()) {
+                    // The first K step overwrites the buffer.
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        if constexpr (PAIR) umma_i8_pair(tmem_d, da + 2 * k, db + 2 * k, kIdesc, k != 0 ? 1u : 0u);
+                        else umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, k != 0 ? 1u : 0u);
+                    }
+                    if constexpr (PAIR) {
+                        umma_commit_pair(map_to_cta(smem_u32(&done_h[s]), 0));
+                        umma_commit_pair(map_to_cta(smem_u32(&done_h[s]), 1));
+                    } else {
+                        umma_commit(&done_h[s]);
+                    }
+                }
+                __syncwarp();
+                s += kStep;
                 if (s >= STAGES) s -= STAGES, ph ^= 1;
-                buf += NISS;
+                buf += kStep;
                 if (buf >= NBUF) buf -= NBUF, bph ^= 1;
             }
         }
@@ -294,27 +361,29 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         // ------------------------------------------------------------------ promotion + epilogue warps
         setmaxnreg_inc<kPromoRegs>();
         const int quarter = warp & 3;
-        const int cg = (warp - 4) >> 2;  // column half of the tile
+        const int cg = (warp - 4) >> 2;  // which SEGW columns of every half this warp owns
         // Tensor-memory address of this warp's lanes and first column in partial buffer 0 (buffer b is b * BN
-        // columns further).  GI8_PIN keeps such loop-invariant values in a register: left alone, the compiler
-        // re-derives them from %tid.x inside the K loop, in a loop whose bound is instruction issue.
-        uint32_t tm_warp = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(cg * CW);
+        // columns further, half h another h * NSUB).  GI8_PIN keeps such loop-invariant values in a register: left
+        // alone, the compiler re-derives them from %tid.x inside the K loop, in a loop whose bound is instruction
+        // issue.
+        uint32_t tm_warp = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + static_cast<uint32_t>(cg * SEGW);
         GI8_PIN(tm_warp);
-        const int half = SPLIT == 2 ? cg : 0;
-        uint32_t bar_done_h = smem_u32(&bar_done[half][0]);
-        uint32_t bar_empty_h = smem_u32(&bar_part_empty[half][0]);
-        GI8_PIN(bar_done_h);
-        GI8_PIN(bar_empty_h);
+        uint32_t bar_done_0 = smem_u32(&bar_done[0][0]);
+        // (PAIR: the hand-back barriers are the leader's, addressed through the cluster window)
+        uint32_t bar_empty_0 = PAIR ? map_to_cta(smem_u32(&bar_part_empty[0][0]), 0) : smem_u32(&bar_part_empty[0][0]);
+        GI8_PIN(bar_done_0);
+        GI8_PIN(bar_empty_0);
         // Stage, partial buffer and barrier phase of the running K block (as in the MMA issuer), stepped without
         // divisions: byte offset of the stage's barrier, its parity, byte offset of the buffer's barrier, the
         // buffer's first column.
         uint32_t st_off = 0, st_par = 0, buf_off = 0, buf_col = 0;
         bool ok = true;
 
-        // Waits for the partial of the running K block; false on every lane if any lane gave up.  The common case is
-        // one successful test; the branch to the bounded spin is taken on a vote, which makes it warp-uniform.
-        auto wait_partial = [&]() {
-            const uint32_t bar = bar_done_h + st_off;
+        // Waits for half h of the partial of the running K block; false on every lane if any lane gave up.  The
+        // common case is one successful test; the branch to the bounded spin is taken on a vote, which makes it
+        // warp-uniform.
+        auto wait_partial = [&](int h) {
+            const uint32_t bar = bar_done_0 + h * (STAGES * 8) + st_off;
             bool got = mbar_try_wait_addr(bar, st_par);
             if (!__all_sync(0xffffffffu, got)) {
                 got = wait_or_abort_addr(bar, st_par, &abort_flag);
@@ -325,11 +394,16 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             tcgen05_fence_after_sync();
             return true;
         };
-        // The whole partial buffer of the running K block is in registers: hand it back to the MMA issuer.
-        auto release_partial = [&]() {
+        // This warp's columns of half h of the running K block are in registers: one of the arrivals that hand the
+        // half back to its MMA issuer.
+        auto release_partial = [&](int h) {
             tcgen05_fence_before_sync();
             __syncwarp();
-            mbar_arrive_elected_addr(bar_empty_h + buf_off);
+            if constexpr (PAIR) {
+                if (elect_one()) mbar_arrive_cluster(bar_empty_0 + h * (NBUF * 8) + buf_off);
+            } else {
+                mbar_arrive_elected_addr(bar_empty_0 + h * (NBUF * 8) + buf_off);
+            }
         };
         auto next_k_block = [&]() {
             st_off += 8;
@@ -338,63 +412,80 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             if (buf_off == NBUF * 8) buf_off = 0, buf_col = 0;
         };
 
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
             int mb, nb;
             tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
-            const int row = mb * kBM + quarter * 32 + lane;
+            const int row = mb * kTileM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
-            const int col_base = nb * BN + cg * CW;  // first output column of this warp
-            // A column half lies inside one 128-wide weight-scale block (CW divides 128, col_base % CW == 0).
-            const bool cols_ok = col_base < p.N;
-            // 32-bit element offsets (the scale arrays are far smaller than 2^31 elements) instead of two pointers.
+            // First output column of this warp's segment in half 0 (half h: kSegStrideH further).  A segment lies
+            // inside one 128-wide weight-scale block (SEGW divides 128 and the segment starts at a multiple of it).
+            const int col_base = nb * BN + cg * kSegStrideCg;
+            // 32-bit element offsets (the scale arrays are far smaller than 2^31 elements) instead of pointers.
             uint32_t sa_off = static_cast<uint32_t>(row_ok ? row : 0) * static_cast<uint32_t>(p.ld_sa);
-            uint32_t sw_off = static_cast<uint32_t>(cols_ok ? col_base / 128 : 0) * static_cast<uint32_t>(p.ld_sw);
+            uint32_t sw_off[SPLIT];
+#pragma unroll
+            for (int h = 0; h < SPLIT; ++h) {
+                const int c = col_base + h * kSegStrideH;
+                sw_off[h] = static_cast<uint32_t>(c < p.N ? c / 128 : 0) * static_cast<uint32_t>(p.ld_sw);
+                GI8_PIN(sw_off[h]);
+            }
             GI8_PIN(sa_off);
-            GI8_PIN(sw_off);
 
-            uint64_t acc[CW / 2];  // fp32 accumulators of columns (2j, 2j + 1) as f32x2 pairs
+            uint64_t acc[CW / 2];  // fp32 accumulators as f32x2 pairs: segment h, columns (2j, 2j + 1) in acc[h * SEGW / 2 + j]
 #pragma unroll
             for (int j = 0; j < CW / 2; ++j) acc[j] = 0ull;
 
             // Scales are loaded two K blocks before their use (an L2 hit takes about one K block); the two register
             // sets alternate statically through the unrolled loop below.
-            float sa0 = 0.0f, sw0 = 0.0f, sa1 = 0.0f, sw1 = 0.0f;
-            sa0 = __ldg(p.sa + sa_off);
-            sw0 = __ldg(p.sw + sw_off);
-            if (num_kb > 1) {
-                sa1 = __ldg(p.sa + (sa_off + 1));
-                sw1 = __ldg(p.sw + (sw_off + 1));
+            float sa_q[2], sw_q[2][SPLIT];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                sa_q[j] = 0.0f;
+#pragma unroll
+                for (int h = 0; h < SPLIT; ++h) sw_q[j][h] = 0.0f;
+                if (j < num_kb) {
+                    sa_q[j] = __ldg(p.sa + (sa_off + j));
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) sw_q[j][h] = __ldg(p.sw + (sw_off[h] + j));
+                }
             }
 
-            // One K block: wait for its partial, form the block's scale (fp32 product, round to nearest) and start
-            // the loads of the scales two blocks on, then per 32-column chunk load, (after the last load) hand the
-            // buffer back, convert and accumulate.
-            auto k_block = [&](int kb, float& sa_r, float& sw_r) -> bool {
-                if (!wait_partial()) return false;
-                const uint64_t t2 = splat_f32x2(sa_r * sw_r);
-                if (kb + 2 < num_kb) {
-                    sa_r = __ldg(p.sa + (sa_off + kb + 2));
-                    sw_r = __ldg(p.sw + (sw_off + kb + 2));
-                }
-                const uint32_t taddr = tm_warp + buf_col;
+            // One K block, scale set j: per half wait for the partial, form the block's scale (fp32 product, round
+            // to nearest), then per 32-column chunk load, (after the half's last load) hand the half back, convert
+            // and accumulate.  The loads of the scales two blocks on are started in between.  (Issuing the next
+            // chunk's load before this chunk's arithmetic was tried: the second register set makes the compiler
+            // spill and the kernel 10-20 % slower.)
+            auto k_block = [&](int kb, int j) -> bool {
+                float t[SPLIT];
 #pragma unroll
-                for (int c = 0; c < NC; ++c) {
-                    uint32_t v[32];
-                    tmem_ld_32x32b_x32(taddr + c * 32, v);
-                    tmem_ld_wait();
-                    if (c + 1 == NC) release_partial();
+                for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_q[j], sw_q[j][h]);
+                const bool more = kb + 2 < num_kb;
+                if (more) sa_q[j] = __ldg(p.sa + (sa_off + kb + 2));
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) promote_pair(acc[c * 16 + j], v[2 * j], v[2 * j + 1], t2);
+                for (int h = 0; h < SPLIT; ++h) {
+                    if (!wait_partial(h)) return false;
+                    if (more) sw_q[j][h] = __ldg(p.sw + (sw_off[h] + kb + 2));
+                    const uint64_t t2 = splat_f32x2(t[h]);
+                    const uint32_t taddr = tm_warp + buf_col + h * NSUB;
+#pragma unroll
+                    for (int c = 0; c < NC; ++c) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(taddr + c * 32, v);
+                        tmem_ld_wait();
+                        if (c + 1 == NC) release_partial(h);
+#pragma unroll
+                        for (int q = 0; q < 16; ++q) promote_pair(acc[h * (SEGW / 2) + c * 16 + q], v[2 * q], v[2 * q + 1], t2);
+                    }
                 }
                 next_k_block();
                 return true;
             };
             for (int kb = 0; kb < num_kb; kb += 2) {
-                if (!k_block(kb, sa0, sw0)) {
+                if (!k_block(kb, 0)) {
                     ok = false;
                     break;
                 }
-                if (kb + 1 < num_kb && !k_block(kb + 1, sa1, sw1)) {
+                if (kb + 1 < num_kb && !k_block(kb + 1, 1)) {
                     ok = false;
                     break;
                 }
@@ -409,13 +500,14 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 int tile_again = tile, mb2, nb2;
                 asm volatile("" : "+r"(tile_again));
                 tile_coords(tile_again, p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
-                const int row0 = mb2 * kBM + quarter * 32;
-                const int col0 = nb2 * BN + cg * CW;
+                const int row0 = mb2 * kTileM + static_cast<int>(rank) * kBM + quarter * 32;
                 if (row0 < p.M) {
                     const uint32_t stg = ((smem_u32(smem_raw) + 1023u) & ~1023u) + STAGES * kStageBytes + (warp - 4) * kStoreBytes;
 #pragma unroll
                     for (int b = 0; b < CW / STORE_W; ++b) {
-                        if (col0 + b * STORE_W >= p.N) break;  // warp-uniform
+                        // box b: segment b / (SEGW / STORE_W), box b % (SEGW / STORE_W) inside it
+                        const int col0 = nb2 * BN + cg * kSegStrideCg + (b / (SEGW / STORE_W)) * kSegStrideH + (b % (SEGW / STORE_W)) * STORE_W;
+                        if (col0 >= p.N) continue;  // warp-uniform
                         if (lane == 0) tma_store_wait_read<0>();  // the previous block has been read out of the staging
                         __syncwarp();
                         // row = lane; 16-byte chunk q of the row goes to chunk q ^ (row % 8) (128-byte swizzle) or
@@ -437,26 +529,32 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                             for (int o = 0; o < p.n_out; ++o)
                                 asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
                                                  reinterpret_cast<uint64_t>(&outs.m[o])),
-                                             "r"(stg), "r"(p.out_col0 + col0 + b * STORE_W), "r"(row0)
+                                             "r"(stg), "r"(p.out_col0 + col0), "r"(row0)
                                              : "memory");
                             tma_store_commit();
                         }
                     }
                 }
-            } else if (row_ok && cols_ok) {
-                uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + col_base;
-                if (col_base + CW <= p.N && p.vec_ok) {
+            } else if (row_ok) {
 #pragma unroll
-                    for (int j = 0; j < CW / 2; j += 4)
-                        *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(pack_bf16x2_of(acc[j]), pack_bf16x2_of(acc[j + 1]),
-                                                                            pack_bf16x2_of(acc[j + 2]), pack_bf16x2_of(acc[j + 3]));
-                } else {
+                for (int h = 0; h < SPLIT; ++h) {
+                    const int c0 = col_base + h * kSegStrideH;
+                    if (c0 >= p.N) continue;
+                    uint16_t* dst = static_cast<uint16_t*>(p.out) + static_cast<int64_t>(row) * p.ldo + c0;
+                    const uint64_t* a = acc + h * (SEGW / 2);
+                    if (c0 + SEGW <= p.N && p.vec_ok) {
 #pragma unroll
-                    for (int j = 0; j < CW / 2; ++j) {
-                        float lo, hi;
-                        unpack_f32x2(acc[j], lo, hi);
-                        if (col_base + 2 * j < p.N) dst[2 * j] = to_bf16_bits(lo);
-                        if (col_base + 2 * j + 1 < p.N) dst[2 * j + 1] = to_bf16_bits(hi);
+                        for (int j = 0; j < SEGW / 2; j += 4)
+                            *reinterpret_cast<uint4*>(dst + 2 * j) = make_uint4(pack_bf16x2_of(a[j]), pack_bf16x2_of(a[j + 1]),
+                                                                                pack_bf16x2_of(a[j + 2]), pack_bf16x2_of(a[j + 3]));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < SEGW / 2; ++j) {
+                            float lo, hi;
+                            unpack_f32x2(a[j], lo, hi);
+                            if (c0 + 2 * j < p.N) dst[2 * j] = to_bf16_bits(lo);
+                            if (c0 + 2 * j + 1 < p.N) dst[2 * j + 1] = to_bf16_bits(hi);
+                        }
                     }
                 }
             }
@@ -467,10 +565,12 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
     tcgen05_fence_before_sync();
     __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();  // neither CTA leaves while the other may still read or signal it
     if (warp == 2) {
         __syncwarp();
         tcgen05_fence_after_sync();
-        tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
+        else tmem_dealloc(tmem_base, kTmemCols);
     }
 }
 

@@ -167,22 +167,26 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
+    // The producer and the MMA issuer run their loops with the WHOLE warp (uniform control flow) and elect one lane
+    // only around the TMA / MMA / commit instructions.  Inside an `if (lane == 0)` region the compiler treats
+    // addresses and descriptors as per-thread values and moves them into uniform registers one by one for every
+    // tcgen05.mma: four MMAs plus a commit then cost about 440 cycles to issue on an idle SM against about 200 in
+    // this form, with 512 cycles of tensor-core work per K block.
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
-        if (lane == 0) {
-            uint32_t it = 0;  // running stage counter across tiles
-            bool ok = true;
-            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
-                int mb, nb;
-                tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
-                    if (!wait_or_abort(&bar_empty[s], ph ^ 1, &abort_flag)) {
-                        raise_error(p.status, &abort_flag, ERR_TIMEOUT_PRODUCER);
-                        ok = false;
-                        break;
-                    }
+        uint32_t s = 0, ph = 0;  // stage and phase parity of the running K-block counter
+        uint32_t armed = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
+            int mb, nb;
+            tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!wait_or_abort(&bar_empty[s], ph ^ 1, &abort_flag)) {
+                    if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_PRODUCER);
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
                     uint8_t* sa = smem + s * kStageBytes;
                     uint8_t* sb = sa + kBytesA;
                     if constexpr (PAIR) {
@@ -197,38 +201,41 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                         tma_load_2d(sb, &map_y, &bar_full[s], kb * kBK, nb * BN);
                     }
                 }
+                __syncwarp();
+                if (armed < STAGES) ++armed;
+                if (++s == STAGES) s = 0, ph ^= 1;
             }
-            // Drain: every armed stage must have landed before the CTA may exit (PAIR: the leader's barriers
-            // complete only when both CTAs' bytes have landed; the peer leaves through the final cluster barrier).
-            const uint32_t armed = (PAIR && rank != 0) ? 0u : (it < STAGES ? it : STAGES);
-            for (uint32_t j = 0; j < armed; ++j) {
-                const uint32_t i2 = it - 1 - j;
-                if (!mbar_wait(&bar_full[i2 % STAGES], (i2 / STAGES) & 1)) {
-                    raise_error(p.status, &abort_flag, ERR_TIMEOUT_DRAIN);
-                    break;
-                }
+        }
+        // Drain: every armed stage must have landed before the CTA may exit (PAIR: the leader's barriers complete
+        // only when both CTAs' bytes have landed; the peer leaves through the final cluster barrier).  (s, ph) is the
+        // slot after the last armed one; walk backwards.
+        if (PAIR && rank != 0) armed = 0;
+        for (uint32_t j = 0; j < armed; ++j) {
+            if (s == 0) s = STAGES, ph ^= 1;
+            --s;
+            if (!mbar_wait(&bar_full[s], ph)) {
+                if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_DRAIN);
+                break;
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0 && rank == 0) {
-            uint32_t it = 0;
+        if (rank == 0) {
+            uint32_t s = 0, ph = 0;
             uint32_t local_tile = 0;
             bool ok = true;
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step, ++local_tile) {
                 const uint32_t buf = local_tile & 1;
                 const uint32_t acc_ph = (local_tile >> 1) & 1;
                 if (!wait_or_abort(&bar_acc_empty[buf], acc_ph ^ 1, &abort_flag)) {
-                    raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
+                    if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
                     break;
                 }
                 tcgen05_fence_after_sync();
                 const uint32_t tmem_d = tmem_base + buf * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
-                    const uint32_t s = it % STAGES;
-                    const uint32_t ph = (it / STAGES) & 1;
+                for (int kb = 0; kb < num_kb; ++kb) {
                     if (!wait_or_abort(&bar_full[s], ph, &abort_flag)) {
-                        raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
+                        if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_MMA);
                         ok = false;
                         break;
                     }
@@ -236,21 +243,25 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                     const uint32_t a_addr = smem_u32(smem + s * kStageBytes);
                     const uint64_t da = make_smem_desc_k128(a_addr);
                     const uint64_t db = make_smem_desc_k128(a_addr + kBytesA);
+                    if (elect_one()) {
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k) {
-                        // +2 in the start-address field = +32 bytes = one UMMA K step inside the swizzled row
-                        if constexpr (PAIR) umma_i8_pair(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0);
-                        else umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0);
+                        for (int k = 0; k < kBK / kUmmaK; ++k) {
+                            // +2 in the start-address field = +32 bytes = one UMMA K step inside the swizzled row
+                            if constexpr (PAIR) umma_i8_pair(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0);
+                            else umma_i8(tmem_d, da + 2 * k, db + 2 * k, kIdesc, (kb | k) != 0);
+                        }
+                        // frees the stage (in both CTAs) once these MMAs have read it
+                        if constexpr (PAIR) {
+                            umma_commit_pair(map_to_cta(smem_u32(&bar_empty[s]), 0));
+                            umma_commit_pair(map_to_cta(smem_u32(&bar_empty[s]), 1));
+                        } else {
+                            umma_commit(&bar_empty[s]);
+                        }
                     }
-                    // frees the stage (in both CTAs) once these MMAs have read it
-                    if constexpr (PAIR) {
-                        umma_commit_pair(map_to_cta(smem_u32(&bar_empty[s]), 0));
-                        umma_commit_pair(map_to_cta(smem_u32(&bar_empty[s]), 1));
-                    } else {
-                        umma_commit(&bar_empty[s]);
-                    }
+                    __syncwarp();
+                    if (++s == STAGES) s = 0, ph ^= 1;
                 }
-                if (ok) {
+                if (ok && elect_one()) {
                     if constexpr (PAIR) {
                         umma_commit_pair(map_to_cta(smem_u32(&bar_acc_full[buf]), 0));
                         umma_commit_pair(map_to_cta(smem_u32(&bar_acc_full[buf]), 1));
@@ -258,6 +269,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
                         umma_commit(&bar_acc_full[buf]);
                     }
                 }
+                __syncwarp();
             }
         }
     } else {

@@ -451,9 +451,12 @@ GI8_DEVICE void umma_commit_pair(uint32_t bar_cluster_addr)
                  : "memory");
 }
 
+// Arrival on a barrier in (possibly) another CTA of the cluster, default semantics (release at CTA scope): what orders
+// the tensor-memory accesses around it is the tcgen05 fence the caller issues, and a cluster-scope release costs a
+// cluster-wide memory fence per arrival.
 GI8_DEVICE void mbar_arrive_cluster(uint32_t bar_cluster_addr)
 {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster_addr) : "memory");
 }
 
 GI8_DEVICE void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols)

@@ -237,7 +237,7 @@ def bw_knobs(g, monkeypatch):
 
 
 @pytest.mark.parametrize("issuers", [1, 2])
-@pytest.mark.parametrize("variant", ["dense_bn64", "dense_bn128", "dense_bn256", None])
+@pytest.mark.parametrize("variant", ["dense_bn64", "dense_bn128", "dense_bn256", "pair", None])
 def test_blockwise_edge_shapes(g, oracle, variant, issuers, bw_knobs):
     bw_knobs(1, issuers)
     g.force_variant(variant)
@@ -264,7 +264,7 @@ def test_blockwise_mma_forms_agree(g, oracle, halves, issuers, bw_knobs):
     (the barrier rings wrap many times)."""
     bw_knobs(halves, issuers)
     gen = torch.Generator().manual_seed(52)
-    for variant in ("dense_bn64", "dense_bn128", "dense_bn256"):
+    for variant in ("dense_bn64", "dense_bn128", "dense_bn256", "pair"):
         g.force_variant(variant)
         for (M, N, K) in [(130, 264, 400), (300, 1000, 2048), (140, 520, 8192)]:
             KB, NB = -(-K // 128), -(-N // 128)
