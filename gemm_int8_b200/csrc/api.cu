@@ -56,15 +56,16 @@ std::atomic<int> g_forced_variant{VAR_AUTO};
 //   GEMM_INT8_TMA_STORE  = 0       bf16 epilogues store from registers instead of through shared memory + TMA
 //   GEMM_INT8_PDL        = 0       small-M kernels are launched without programmatic dependent launch
 //   GEMM_INT8_SPLITS     = n       small-M kernels: number of K splits
-//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256, or (default) two column halves with N = 128
-//   GEMM_INT8_BW_ISSUERS = 1 | 2   blockwise kernel without column halves: MMA-issuing threads (default 2)
+//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256 (default), or two column halves with N = 128
+//   GEMM_INT8_BW_ISSUERS = 1 | 2   blockwise kernel without column halves: MMA-issuing threads (default: one for the
+//                                  256-wide tile, two for the narrower ones, whose MMAs are issue bound)
 struct Knobs {
     int group_m = 0;
     bool tma_store = true;
     bool pdl = true;
     int splits = 0;
-    int bw_halves = 2;
-    int bw_issuers = 2;
+    int bw_halves = 1;
+    int bw_issuers = 0;  // 0: one for the 256-wide tile, two for the narrower ones
 };
 Knobs g_knobs;
 std::once_flag g_knobs_once;
@@ -79,8 +80,8 @@ void load_knobs()
     if (const char* e = getenv("GEMM_INT8_TMA_STORE")) k.tma_store = e[0] != '0';
     if (const char* e = getenv("GEMM_INT8_PDL")) k.pdl = e[0] != '0';
     if (const char* e = getenv("GEMM_INT8_SPLITS")) k.splits = atoi(e);
-    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 1 ? 1 : 2;
-    if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 1 ? 1 : 2;
+    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 2 ? 2 : 1;
+    if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 2 ? 2 : atoi(e) == 1 ? 1 : 0;
     g_knobs = k;
 }
 
@@ -222,25 +223,46 @@ int check_common(const void* x, const void* y, const void* out, int64_t M, int64
 }
 
 // ---------------------------------------------------------------------------------------------------
-// Dispatch: picks the tile width for the dense/blockwise kernels.  Model fitted on B200: the grid runs
-// ceil(tiles / SMs) waves; a wave of 128 x BN tiles costs BN x c(BN) + a fixed part per K block, where c is the
-// measured inefficiency of the narrower tensor-core instruction (its shared-memory operand traffic per MAC is
-// higher): dense 2900 / 1750 / 1000 TOP/s and blockwise 1900 / 1520 / 850 TOP/s at BN = 256 / 128 / 64.
+// Dispatch: picks the tile form for the dense/blockwise kernels (replaces the reference's five-branch shape table,
+// csrc/kernels/gemm.cu:136-161).  Model: the persistent grid runs ceil(tiles / slots) waves, and a wave costs the
+// form's cycles per K block, fitted on B200 from device-timed runs (8192^3, 2048 x 11008 x 4096, 128..512 x 8192 x
+// 8192 and the reference benchmark's layer shapes, timed back to back):
+//   dense      256 x 256 two-CTA tile (74 slots) 580 | 128 x 256: 655 | 128 x 128: 465 | 128 x 64: 330
+//   blockwise  128 x 256: 930 | 128 x 128: 670 | 128 x 64: 490   (the two-CTA form measures the same as 128 x 256
+//              and stays a selectable variant)
+// The table is data: kTileForms below.  The narrow tiles cost more per column (the tensor-core instruction is issue
+// bound below N = 128, and the per-K-block hand-overs do not shrink with the tile) and only pay when the wide tile
+// would leave most SMs without work.
 // ---------------------------------------------------------------------------------------------------
+struct TileForm {
+    int bn;
+    bool pair;
+    double kblock_cycles;
+};
+constexpr TileForm kDenseForms[] = {{256, true, 580.0}, {256, false, 655.0}, {128, false, 465.0}, {64, false, 330.0}};
+constexpr TileForm kBlockwiseForms[] = {{256, false, 930.0}, {128, false, 670.0}, {64, false, 490.0}};
+
 int pick_bn(int64_t M, int64_t N, int sms, bool blockwise, bool* pair = nullptr)
 {
     if (pair) *pair = false;
-    const int cand[3] = {256, 128, 64};
-    const double ineff_dense[3] = {1.0, 1.65, 2.9};
-    const double ineff_block[3] = {1.0, 1.35, 2.4};
+    const TileForm* forms = blockwise ? kBlockwiseForms : kDenseForms;
+    const int n_forms = blockwise ? 3 : 4;
     int best = 256;
     double best_cost = 1e300;
-    for (int i = 0; i < 3; ++i) {
-        const int bn = cand[i];
-        const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
-        const int64_t waves = (tiles + sms - 1) / sms;
-        const double cost = static_cast<double>(waves) * (bn * (blockwise ? ineff_block[i] : ineff_dense[i]) + 16.0);
-        if (cost < best_cost) best_cost = cost, best = bn;
+    for (int i = 0; i < n_forms; ++i) {
+        const TileForm& f = forms[i];
+        if (f.pair && !pair) continue;  // the caller has no two-CTA form
+        const int tile_m = f.pair ? 2 * kBM : kBM;
+        const int64_t tiles = ((M + tile_m - 1) / tile_m) * ((N + f.bn - 1) / f.bn);
+        const int64_t slots = f.pair ? sms / 2 : sms;
+        const int64_t waves = (tiles + slots - 1) / slots;
+        // (a wave also pays a fixed part per tile: prologue, epilogue, tile turnover -- about 20 K blocks' worth at
+        // K = 4096; the model only ranks forms for one K, so it enters as a small constant)
+        const double cost = static_cast<double>(waves) * (f.kblock_cycles + 16.0);
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost, best = f.bn;
+            if (pair) *pair = f.pair;
+        }
     }
     return best;
 }
@@ -348,12 +370,14 @@ int dispatch_dense(DeviceState* st, const int8_t* x, const int8_t* y, DenseParam
     const int forced = g_forced_variant;
     if (forced == VAR_PAIR) return launch_dense_pair<EPI>(st, 45 + EPI, x, y, p, stream);
     int bn;
+    bool pair = false;
     switch (forced) {
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
         case VAR_DENSE_BN64: bn = 64; break;
-        default: bn = pick_bn(p.M, p.N, st->sm_count, false);
+        default: bn = pick_bn(p.M, p.N, st->sm_count, false, &pair);
     }
+    if (pair) return launch_dense_pair<EPI>(st, 45 + EPI, x, y, p, stream);
     if (bn == 256) return launch_dense<256, 4, EPI>(st, EPI * 3 + 0, x, y, p, stream);
     if (bn == 128) return launch_dense<128, 6, EPI>(st, EPI * 3 + 1, x, y, p, stream);
     return launch_dense<64, 8, EPI>(st, EPI * 3 + 2, x, y, p, stream);
@@ -565,8 +589,9 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
         const int bn = pick_bn(M, N, sms, true);
         return bn == 256 ? "blockwise_bn256" : bn == 128 ? "blockwise_bn128" : "blockwise_bn64";
     }
-    const int bn = pick_bn(M, N, sms, false);
-    return bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
+    bool pair = false;
+    const int bn = pick_bn(M, N, sms, false, &pair);
+    return pair ? "pair" : bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
 }
 
 int gi8_reload_env(void)
@@ -910,7 +935,7 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         cfg.numAttrs = 1;                                                                     \
         GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mx, my, mo, p));                            \
     } while (0)
-    const bool two = knobs().bw_issuers == 2;
+    const bool two = knobs().bw_issuers == 2 || (knobs().bw_issuers == 0 && bn < 256);
     const bool halves = knobs().bw_halves == 2;
     if (pair) {
         if (halves) GI8_LAUNCH_BW(256, 6, 2, 2, true, 21);

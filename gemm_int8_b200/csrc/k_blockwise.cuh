@@ -453,8 +453,9 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             // One K block, scale set j: per half wait for the partial, form the block's scale (fp32 product, round
             // to nearest), then per 32-column chunk load, (after the half's last load) hand the half back, convert
             // and accumulate.  The loads of the scales two blocks on are started in between.  (Issuing the next
-            // chunk's load before this chunk's arithmetic was tried: the second register set makes the compiler
-            // spill and the kernel 10-20 % slower.)
+            // chunk's load before this chunk's arithmetic was tried with 32- and with 16-column chunks: no gain, the
+            // 32-column form spills.  Sending a third of the pairs through an integer multiply-add on the other pipe
+            // instead of cvt was tried too: no gain.)
             auto k_block = [&](int kb, int j) -> bool {
                 float t[SPLIT];
 #pragma unroll

@@ -107,11 +107,19 @@ class FusedGatherGemm:
     [M, N] matrix (TMA stores through mapped peer memory), so the all-gather rides on the GEMM tile by tile and no
     collective or permuting copy follows.
 
-    Set-up (once per output shape): every rank allocates its [M, N] bf16 matrix with the library's peer allocator,
+    Set-up (once per output shape): every rank allocates TWO [M, N] bf16 matrices with the library's peer allocator,
     the CUDA IPC handles are exchanged through `torch.distributed` (object all-gather: host side, any backend), and
-    each rank maps the others' matrices.  Per call: one kernel launch, then a barrier (`torch.distributed.barrier`
-    on the same stream) after which `result()` is complete on every rank.  Ranks must be processes on one node with
-    peer access between their GPUs; no multicast is used.
+    each rank maps the others' matrices.  Per call: one kernel launch, then a barrier after which the returned
+    matrix is complete on every rank.  Ranks must be processes on one node with peer access between their GPUs;
+    no multicast is used.
+
+    Lifetime of a result.  Peers write into this rank's matrix, so a result can be overwritten from outside.  Calls
+    alternate between the two matrices: the matrix returned by call i is written again by call i + 2, and a peer
+    can start its call i + 2 only after the barrier of call i + 1 has completed, i.e. after THIS rank's stream has
+    reached its own barrier of call i + 1.  Hence the rule: consume the result of call i on the stream `run` was
+    called on (or make that stream wait for the consumer) before calling `run` for the second time after it; with
+    that, no cross-rank write-after-read can happen.  The barrier must be stream-ordered (NCCL); with a host-only
+    backend `run` synchronises the stream before the barrier instead.
     """
 
     def __init__(self, M: int, N: int, group=None):
@@ -132,52 +140,61 @@ class FusedGatherGemm:
         if N % 8 or self.lo % 32 or (self.hi % 32 and self.hi != N):
             raise ValueError("N must be a multiple of 8 and every shard a multiple of 32 columns")
         self.device = torch.device("cuda", torch.cuda.current_device())
+        self._stream_ordered = dist.get_backend(group) == "nccl"
         nbytes = M * N * 2
-        own = ctypes.c_void_p()
-        _lib.check(_C, _C.gi8_peer_alloc(ctypes.byref(own), nbytes))
-        self._own = own
-        handle = (ctypes.c_ubyte * 64)()
-        _lib.check(_C, _C.gi8_peer_export(own, handle))
-        handles = [None] * self.world
-        dist.all_gather_object(handles, bytes(handle), group=group)
-        self._mapped = []
-        ptrs = []
-        for r, h in enumerate(handles):
-            if r == self.rank:
-                ptrs.append(own.value)
-                continue
-            buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
-            p = ctypes.c_void_p()
-            _lib.check(_C, _C.gi8_peer_import(buf, ctypes.byref(p)))
-            self._mapped.append(p)
-            ptrs.append(p.value)
-        # own matrix first (the entry point takes any order; outs[0] is only used for argument checks)
-        order = [self.rank] + [r for r in range(self.world) if r != self.rank]
-        self._outs = (ctypes.c_void_p * self.world)(*[ptrs[r] for r in order])
-        self._view = _tensor_from_ptr(own.value, (M, N), self.device)
+        self._own, self._mapped, self._outs, self._views = [], [], [], []
+        for _ in range(2):
+            own = ctypes.c_void_p()
+            _lib.check(_C, _C.gi8_peer_alloc(ctypes.byref(own), nbytes))
+            self._own.append(own)
+            handle = (ctypes.c_ubyte * 64)()
+            _lib.check(_C, _C.gi8_peer_export(own, handle))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(own.value)
+                    continue
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                p = ctypes.c_void_p()
+                _lib.check(_C, _C.gi8_peer_import(buf, ctypes.byref(p)))
+                self._mapped.append(p)
+                ptrs.append(p.value)
+            # own matrix first (the entry point takes any order; outs[0] is only used for argument checks)
+            order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+            self._outs.append((ctypes.c_void_p * self.world)(*[ptrs[r] for r in order]))
+            self._views.append(_tensor_from_ptr(own.value, (M, N), self.device))
+        self._turn = 0
         dist.barrier(group=group)  # every rank has mapped every matrix before anyone writes
 
     def run(self, x_q: torch.Tensor, w_q_shard: torch.Tensor, x_scale: torch.Tensor, w_scale_shard: torch.Tensor,
             barrier: bool = True) -> torch.Tensor:
         """Launches the GEMM on the current stream; with `barrier` also the cross-rank barrier after which the
-        returned [M, N] bf16 tensor (this rank's matrix) is complete."""
+        returned [M, N] bf16 tensor (one of this rank's two matrices) is complete.  See the class docstring for how
+        long the returned tensor stays valid."""
         import torch.distributed as dist
 
         M, K = x_q.shape
         n_local = w_q_shard.shape[0]
         if M != self.M or n_local != self.hi - self.lo:
             raise ValueError("operand shapes do not match the gather buffers")
+        turn = self._turn
+        self._turn ^= 1
         stream = torch.cuda.current_stream(self.device).cuda_stream
         rc = self._C.gi8_matmul_blockwise_allgather(
             x_q.data_ptr(), w_q_shard.data_ptr(), x_scale.data_ptr(), x_scale.stride(0), w_scale_shard.data_ptr(),
-            w_scale_shard.stride(0), self._outs, self.world, M, n_local, K, self.N, self.lo, stream)
+            w_scale_shard.stride(0), self._outs[turn], self.world, M, n_local, K, self.N, self.lo, stream)
         self._lib.check(self._C, rc)
         if barrier:
+            if not self._stream_ordered:
+                torch.cuda.current_stream(self.device).synchronize()  # a host-only barrier orders nothing on the GPU
             dist.barrier(group=self.group)
-        return self._view
+        return self._views[turn]
 
     def result(self) -> torch.Tensor:
-        return self._view
+        """The matrix the most recent `run` wrote."""
+        return self._views[self._turn ^ 1]
 
     def close(self) -> None:
         """Unmaps the peers' matrices and frees this rank's (collective: every rank must call it)."""
@@ -188,11 +205,11 @@ class FusedGatherGemm:
         for p in self._mapped:
             self._lib.check(self._C, self._C.gi8_peer_release(p))
         self._mapped = []
-        self._view = None
+        self._views = []
         dist.barrier(group=self.group)  # nobody frees while a peer still has the matrix mapped
-        if self._own is not None:
-            self._lib.check(self._C, self._C.gi8_peer_free(self._own))
-            self._own = None
+        for own in self._own:
+            self._lib.check(self._C, self._C.gi8_peer_free(own))
+        self._own = []
 
 
 def _tensor_from_ptr(ptr: int, shape, device: torch.device) -> torch.Tensor:

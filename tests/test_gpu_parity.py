@@ -309,13 +309,29 @@ def test_config2_blockwise_prefill_full_size(g, oracle):
 
 
 @pytest.mark.parametrize("K,N", [(8192, 10240), (8192, 8192), (8192, 57344), (28672, 8192)])
-def test_config4_llama70b_shapes_m128(g, oracle, K, N):
-    """Config 4 inputs (outlier channels, Hadamard rotation, blockwise quantisation) at the sweep's smallest M."""
+def test_config4_llama70b_sweep_all_m(g, oracle, K, N):
+    """Config 4 inputs (outlier channels, Hadamard rotation, blockwise quantisation) for every M of the sweep.
+    The oracle computes 128 distinct token rows once per (K, N); M = 128 is compared whole, and for
+    M in {512, 2048, 8192, 16384} the 128 rows are tiled to M rows: the first, a middle and the last 128-row block
+    of the result must each equal the oracle bit for bit (so every row block a CTA can be handed at that size meets
+    the oracle's values at full K depth), and the run must leave the kernel status word clear."""
     from gemm_int8_b200 import workloads
 
     xq, wq, sa, sw = workloads.llama70b(128, N, K)
-    out = g.matmul_blockwise(xq.cuda(), wq.cuda(), sa.cuda(), sw.cuda())
-    assert_bits_equal(oracle, out, oracle.c_matmul_blockwise(xq, wq, sa, sw), f"config 4 K={K} N={N}")
+    ref = oracle.c_matmul_blockwise(xq, wq, sa, sw)
+    xd, wd, sad, swd = xq.cuda(), wq.cuda(), sa.cuda(), sw.cuda()
+    out = g.matmul_blockwise(xd, wd, sad, swd)
+    assert_bits_equal(oracle, out, ref, f"config 4 M=128 K={K} N={N}")
+    del out
+    for M in (512, 2048, 8192, 16384):
+        reps = M // 128
+        x_big, sa_big = xd.repeat(reps, 1), sad.repeat(reps, 1)
+        out = g.matmul_blockwise(x_big, wd, sad.repeat(reps, 1), swd)
+        assert out.shape == (M, N)
+        for blk in sorted({0, reps // 2, reps - 1}):
+            assert_bits_equal(oracle, out[blk * 128:(blk + 1) * 128], ref, f"config 4 M={M} K={K} N={N} row block {blk}")
+        del out, x_big, sa_big
+    assert g.device_status() == 0
 
 
 def test_config5_full_size_sampled_rows_and_properties(g, oracle):

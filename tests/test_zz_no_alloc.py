@@ -5,8 +5,8 @@ library, so the caller passes inputs and outputs only.
 
 The file name sorts last on purpose: under `pytest -x` every other test has run before this one can fail.
 It is self-contained (own inputs, own library handle) and passes alone in a fresh process as well as after
-the rest of the suite.  The result must equal gi8_matmul_scaled (caller-owned workspace) bit for bit -- the
-same bar the other parity tests use -- on two calls in a row that share the static array."""
+the rest of the suite.  The result must equal gi8_matmul_scaled (caller-owned workspace) AND the CPU oracle bit
+for bit -- the same bar the other parity tests use -- on two calls in a row that share the static array."""
 import ctypes
 
 import pytest
@@ -37,30 +37,35 @@ def _call_workspace(C, x, y, sx, sw, stream):
     return out
 
 
-def test_static_scratch_entry_matches_workspace_entry_twice():
+def test_static_scratch_entry_matches_workspace_entry_twice(oracle):
     import gemm_int8_b200 as g
 
     C = g._C
     g.force_variant("smallm")    # the comparison entry point then runs the same split-K kernel with caller scratch
-    dev = torch.device("cuda", 0)
-    torch.cuda.set_device(dev)
-    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    gen = torch.Generator().manual_seed(2718)
-    # two calls in a row with different shapes and data: the second must not see the first one's leftovers
-    for (M, N, K) in [(16, 4096, 4096), (48, 1000, 2048)]:
-        x = torch.randint(-128, 128, (M, K), dtype=torch.int8, generator=gen).to(dev)
-        y = torch.randint(-128, 128, (N, K), dtype=torch.int8, generator=gen).to(dev)
-        sx = (torch.rand(M, generator=gen) * 0.05 + 1e-3).to(dev)
-        sw = (torch.rand(N, generator=gen) * 0.05 + 1e-3).to(dev)
-        assert int(C.gi8_matmul_scaled_workspace_bytes(M, N, K)) > 0, "shape must exercise the split-K scratch"
-        expect = _call_workspace(C, x, y, sx, sw, stream)
-        got = _call_static(C, x, y, sx, sw, stream)
-        torch.cuda.synchronize()
-        assert torch.equal(got.view(torch.int16), expect.view(torch.int16))
-        again = _call_static(C, x, y, sx, sw, stream)       # same inputs, straight after
-        torch.cuda.synchronize()
-        assert torch.equal(again.view(torch.int16), expect.view(torch.int16))
-    g.force_variant(None)
+    try:
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        gen = torch.Generator().manual_seed(2718)
+        # two calls in a row with different shapes and data: the second must not see the first one's leftovers
+        for (M, N, K) in [(16, 4096, 4096), (48, 1000, 2048)]:
+            xc = torch.randint(-128, 128, (M, K), dtype=torch.int8, generator=gen)
+            yc = torch.randint(-128, 128, (N, K), dtype=torch.int8, generator=gen)
+            sxc = torch.rand(M, generator=gen) * 0.05 + 1e-3
+            swc = torch.rand(N, generator=gen) * 0.05 + 1e-3
+            x, y, sx, sw = xc.to(dev), yc.to(dev), sxc.to(dev), swc.to(dev)
+            assert int(C.gi8_matmul_scaled_workspace_bytes(M, N, K)) > 0, "shape must exercise the split-K scratch"
+            expect = _call_workspace(C, x, y, sx, sw, stream)
+            got = _call_static(C, x, y, sx, sw, stream)
+            torch.cuda.synchronize()
+            assert torch.equal(got.view(torch.int16), expect.view(torch.int16))
+            again = _call_static(C, x, y, sx, sw, stream)       # same inputs, straight after
+            torch.cuda.synchronize()
+            assert torch.equal(again.view(torch.int16), expect.view(torch.int16))
+            ref_bits = oracle.c_matmul_scaled(xc, yc, sxc, swc)  # the CPU restatement, independent of both entry points
+            assert (oracle.bf16_bits(got) == ref_bits).all() and (oracle.bf16_bits(again) == ref_bits).all()
+    finally:
+        g.force_variant(None)
     assert g.device_status() == 0
 
 
