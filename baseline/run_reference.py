@@ -3,7 +3,7 @@ from the reference's unmodified csrc/kernels/gemm.cu and bindings.cpp) on seeded
 its own: the library registers the torch namespace gemm_int8_CUDA, which this repository's package also
 defines, so the two cannot live in one interpreter.  This file never imports the product package.
 
-    python baseline/run_reference.py --cases cases.json --out results.npz [--time]
+    python baseline/run_reference.py --cases cases.json --out results.npz [--time [--no-outputs]]
 
 cases.json: a list of {"name", "kind", "M", "N", "K", "alpha", "seed"}; kind is one of
   "uniform"   x, y = randint(-128, 127) with seeds seed, seed + 1              (the README example)
@@ -58,6 +58,7 @@ def main() -> int:
     ap.add_argument("--cases", required=True)
     ap.add_argument("--out", required=True)
     ap.add_argument("--time", action="store_true")
+    ap.add_argument("--no-outputs", action="store_true", help="with --time: store the timings only")
     args = ap.parse_args()
     if not available():
         print(f"reference library {REF_LIB} not built (baseline/build_reference.sh)", file=sys.stderr)
@@ -75,7 +76,8 @@ def main() -> int:
         xd, yd = x.to(dev), y.to(dev)
         r = op(xd, yd, float(c["alpha"]))
         torch.cuda.synchronize()
-        out[c["name"]] = r.view(torch.int16).cpu().numpy().view(np.uint16)
+        if not args.no_outputs:
+            out[c["name"]] = r.view(torch.int16).cpu().numpy().view(np.uint16)
         if args.time:
             for _ in range(10):
                 op(xd, yd, float(c["alpha"]))
