@@ -408,7 +408,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
-                    help="N > 1: all-gather fused into the GEMM epilogue (peer stores), or NCCL after it (auto)")
+                    help="N > 1: all-gather fused into the GEMM epilogue (peer stores; auto), or NCCL after it")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -446,7 +446,7 @@ def main():
     if world > 1 and not sharded:
         raise SystemExit("only the blockwise workloads shard over several GPUs")
     if args.gather == "auto":
-        args.gather = "nccl"
+        args.gather = "fused"  # measured faster than GEMM + NCCL all-gather at 2, 4 and 8 GPUs
     if sharded:
         from gemm_int8_b200 import dist as gdist
 
