@@ -99,19 +99,22 @@ GI8_DEVICE void setmaxnreg_dec()
 
 // acc{lo,hi} += fp32(v0, v1) * t for a pair of int32 partials (|P| <= 128 * 128 * 128 = 2^21, so the conversion is
 // exact) as two cvt.rn.f32.s32 and one fma.rn.f32x2; each half of the packed fma rounds like a scalar fmaf.
-GI8_DEVICE void promote_pair(uint64_t& acc, uint32_t v0, uint32_t v1, uint64_t t2)
+// The conversions write back into v0 and v1, which a tensor-memory load left in two consecutive registers: the
+// packed operand of the fma is then that register pair as it stands.  Converting into fresh registers made the
+// compiler add a move or two per pair to bring the results together (measured: 74 extra instructions per warp and
+// K block next to 192 useful ones).
+GI8_DEVICE void promote_pair(uint64_t& acc, uint32_t& v0, uint32_t& v1, uint64_t t2)
 {
     asm volatile(
         "{\n\t"
         ".reg .b64 pv;\n\t"
-        ".reg .f32 a, b;\n\t"
-        "cvt.rn.f32.s32 a, %1;\n\t"
-        "cvt.rn.f32.s32 b, %2;\n\t"
-        "mov.b64 pv, {a, b};\n\t"
+        "cvt.rn.f32.s32 %1, %1;\n\t"
+        "cvt.rn.f32.s32 %2, %2;\n\t"
+        "mov.b64 pv, {%1, %2};\n\t"
         "fma.rn.f32x2 %0, pv, %3, %0;\n\t"
         "}\n"
-        : "+l"(acc)
-        : "r"(v0), "r"(v1), "l"(t2));
+        : "+l"(acc), "+r"(v0), "+r"(v1)
+        : "l"(t2));
 }
 
 GI8_DEVICE uint64_t splat_f32x2(float t)
@@ -125,6 +128,14 @@ GI8_DEVICE uint64_t splat_f32x2(float t)
 // (tensor-memory loads, conversions).  The scales are loaded two K blocks before their use; written as plain C++ the
 // compiler hoists the product up to the loads to save a register, and the warp then waits out the L2 latency right
 // there (measured: 150 cycles per K block).
+// Read-only global load as a volatile statement, for the same reason: the compiler may not sink it towards its use.
+GI8_DEVICE float ldg_in_place(const float* p)
+{
+    float r;
+    asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(r) : "l"(p));
+    return r;
+}
+
 GI8_DEVICE float mul_in_place(float a, float b)
 {
     float r;
@@ -182,7 +193,8 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     constexpr int NSUB = BN / SPLIT;     // N of one MMA = columns of one half
     constexpr int CW = BN / 2;           // columns per promotion warp (128, 64 or 32) ...
     constexpr int SEGW = CW / SPLIT;     // ... as SPLIT segments of SEGW columns, one in each half
-    constexpr int NC = SEGW / 32;        // 32-column loads per segment
+    constexpr int CHW = 32;              // columns per tensor-memory load (64 was measured: no gain)
+    constexpr int NC = SEGW / CHW;       // loads per segment
     constexpr int STORE_W = blockwise_store_cols(BN);
     static_assert(SEGW % STORE_W == 0 && SEGW % 32 == 0, "segments are whole store boxes and whole loads");
     // SPLIT == 1: each issuer must own the stages and the partial buffers of its K blocks (see the protocol above):
@@ -461,21 +473,21 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #pragma unroll
                 for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_q[j], sw_q[j][h]);
                 const bool more = kb + 2 < num_kb;
-                if (more) sa_q[j] = __ldg(p.sa + (sa_off + kb + 2));
+                if (more) sa_q[j] = ldg_in_place(p.sa + (sa_off + kb + 2));
 #pragma unroll
                 for (int h = 0; h < SPLIT; ++h) {
                     if (!wait_partial(h)) return false;
-                    if (more) sw_q[j][h] = __ldg(p.sw + (sw_off[h] + kb + 2));
+                    if (more) sw_q[j][h] = ldg_in_place(p.sw + (sw_off[h] + kb + 2));
                     const uint64_t t2 = splat_f32x2(t[h]);
                     const uint32_t taddr = tm_warp + buf_col + h * NSUB;
 #pragma unroll
                     for (int c = 0; c < NC; ++c) {
-                        uint32_t v[32];
-                        tmem_ld_32x32b_x32(taddr + c * 32, v);
+                        uint32_t v[CHW];
+                        tmem_ld_32x32b_x32(taddr + c * CHW, v);
                         tmem_ld_wait();
                         if (c + 1 == NC) release_partial(h);
 #pragma unroll
-                        for (int q = 0; q < 16; ++q) promote_pair(acc[h * (SEGW / 2) + c * 16 + q], v[2 * q], v[2 * q + 1], t2);
+                        for (int q = 0; q < CHW / 2; ++q) promote_pair(acc[h * (SEGW / 2) + c * (CHW / 2) + q], v[2 * q], v[2 * q + 1], t2);
                     }
                 }
                 next_k_block();
