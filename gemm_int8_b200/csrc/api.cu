@@ -56,7 +56,7 @@ std::atomic<int> g_forced_variant{VAR_AUTO};
 //   GEMM_INT8_TMA_STORE  = 0       bf16 epilogues store from registers instead of through shared memory + TMA
 //   GEMM_INT8_PDL        = 0       small-M kernels are launched without programmatic dependent launch
 //   GEMM_INT8_SPLITS     = n       small-M kernels: number of K splits
-//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256 (default), or two column halves with N = 128
+//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256, or (default) two column halves with N = 128
 //   GEMM_INT8_BW_ISSUERS = 1 | 2   blockwise kernel without column halves: MMA-issuing threads (default: one for the
 //                                  256-wide tile, two for the narrower ones, whose MMAs are issue bound)
 struct Knobs {
@@ -64,7 +64,7 @@ struct Knobs {
     bool tma_store = true;
     bool pdl = true;
     int splits = 0;
-    int bw_halves = 1;
+    int bw_halves = 2;
     int bw_issuers = 0;  // 0: one for the 256-wide tile, two for the narrower ones
 };
 Knobs g_knobs;
@@ -80,7 +80,7 @@ void load_knobs()
     if (const char* e = getenv("GEMM_INT8_TMA_STORE")) k.tma_store = e[0] != '0';
     if (const char* e = getenv("GEMM_INT8_PDL")) k.pdl = e[0] != '0';
     if (const char* e = getenv("GEMM_INT8_SPLITS")) k.splits = atoi(e);
-    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 2 ? 2 : 1;
+    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 1 ? 1 : 2;
     if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 2 ? 2 : atoi(e) == 1 ? 1 : 0;
     g_knobs = k;
 }
@@ -228,7 +228,7 @@ int check_common(const void* x, const void* y, const void* out, int64_t M, int64
 // form's cycles per K block, fitted on B200 from device-timed runs (8192^3, 2048 x 11008 x 4096, 128..512 x 8192 x
 // 8192 and the reference benchmark's layer shapes, timed back to back):
 //   dense      256 x 256 two-CTA tile (74 slots) 580 | 128 x 256: 655 | 128 x 128: 465 | 128 x 64: 330
-//   blockwise  128 x 256: 930 | 128 x 128: 670 | 128 x 64: 490   (the two-CTA form measures the same as 128 x 256
+//   blockwise  128 x 256: 990 | 128 x 128: 650 | 128 x 64: 490   (the two-CTA form measures the same as 128 x 256
 //              and stays a selectable variant)
 // The table is data: kTileForms below.  The narrow tiles cost more per column (the tensor-core instruction is issue
 // bound below N = 128, and the per-K-block hand-overs do not shrink with the tile) and only pay when the wide tile
@@ -240,7 +240,7 @@ struct TileForm {
     double kblock_cycles;
 };
 constexpr TileForm kDenseForms[] = {{256, true, 580.0}, {256, false, 655.0}, {128, false, 465.0}, {64, false, 330.0}};
-constexpr TileForm kBlockwiseForms[] = {{256, false, 930.0}, {128, false, 670.0}, {64, false, 490.0}};
+constexpr TileForm kBlockwiseForms[] = {{256, false, 990.0}, {128, false, 650.0}, {64, false, 490.0}};
 
 int pick_bn(int64_t M, int64_t N, int sms, bool blockwise, bool* pair = nullptr)
 {
@@ -878,6 +878,8 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
     p.n_out = 1, p.out_col0 = 0;
+    p.scale_vec = (KB % 4 == 0) && (ld_sa % 4 == 0) && (ld_sw % 4 == 0) && reinterpret_cast<uintptr_t>(sa) % 16 == 0 &&
+                  reinterpret_cast<uintptr_t>(sw) % 16 == 0;
     const int forced = g_forced_variant;
     int bn;
     bool pair = false;

@@ -70,6 +70,7 @@ struct BlockwiseParams {
     int n_out;      // number of output matrices the TMA-store epilogue writes every block to (1, or the ranks of an
                     // N-sharded group: each rank's full [M, N_total] matrix, peers through mapped peer memory)
     int out_col0;   // column of this GEMM's first output column in those matrices
+    int scale_vec;  // ceil(K/128) % 4 == 0 and the rows of sa and sw are 16-byte aligned: scales are loaded four at a time
 };
 
 constexpr int kMaxOutputs = 8;
@@ -133,6 +134,13 @@ GI8_DEVICE float ldg_in_place(const float* p)
 {
     float r;
     asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(r) : "l"(p));
+    return r;
+}
+
+GI8_DEVICE float4 ldg4_in_place(const float* p)
+{
+    float4 r;
+    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(r.x), "=f"(r.y), "=f"(r.z), "=f"(r.w) : "l"(p));
     return r;
 }
 
@@ -447,37 +455,16 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #pragma unroll
             for (int j = 0; j < CW / 2; ++j) acc[j] = 0ull;
 
-            // Scales are loaded two K blocks before their use (an L2 hit takes about one K block); the two register
-            // sets alternate statically through the unrolled loop below.
-            float sa_q[2], sw_q[2][SPLIT];
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                sa_q[j] = 0.0f;
-#pragma unroll
-                for (int h = 0; h < SPLIT; ++h) sw_q[j][h] = 0.0f;
-                if (j < num_kb) {
-                    sa_q[j] = __ldg(p.sa + (sa_off + j));
-#pragma unroll
-                    for (int h = 0; h < SPLIT; ++h) sw_q[j][h] = __ldg(p.sw + (sw_off[h] + j));
-                }
-            }
-
-            // One K block, scale set j: per half wait for the partial, form the block's scale (fp32 product, round
-            // to nearest), then per 32-column chunk load, (after the half's last load) hand the half back, convert
-            // and accumulate.  The loads of the scales two blocks on are started in between.  (Issuing the next
-            // chunk's load before this chunk's arithmetic was tried with 32- and with 16-column chunks: no gain, the
-            // 32-column form spills.  Sending a third of the pairs through an integer multiply-add on the other pipe
-            // instead of cvt was tried too: no gain.)
-            auto k_block = [&](int kb, int j) -> bool {
-                float t[SPLIT];
-#pragma unroll
-                for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_q[j], sw_q[j][h]);
-                const bool more = kb + 2 < num_kb;
-                if (more) sa_q[j] = ldg_in_place(p.sa + (sa_off + kb + 2));
+            // One K block with the scale products t[h] of its column halves: per half wait for the partial, then per
+            // 32-column chunk load, (after the half's last load) hand the half back, convert and accumulate.
+            // (Issuing the next chunk's load before this chunk's arithmetic was tried with 32- and with 16-column
+            // chunks: no gain, the 32-column form spills.  64-column loads: no gain.  Sending a third of the pairs
+            // through an integer multiply-add on the other pipe instead of cvt: no gain.  Leaving the grouping of
+            // conversions and multiply-adds to the compiler (non-volatile statements): the same cycle count.)
+            auto k_block = [&](const float (&t)[SPLIT]) -> bool {
 #pragma unroll
                 for (int h = 0; h < SPLIT; ++h) {
                     if (!wait_partial(h)) return false;
-                    if (more) sw_q[j][h] = ldg_in_place(p.sw + (sw_off[h] + kb + 2));
                     const uint64_t t2 = splat_f32x2(t[h]);
                     const uint32_t taddr = tm_warp + buf_col + h * NSUB;
 #pragma unroll
@@ -493,14 +480,70 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 next_k_block();
                 return true;
             };
-            for (int kb = 0; kb < num_kb; kb += 2) {
-                if (!k_block(kb, 0)) {
-                    ok = false;
-                    break;
+
+            if (p.scale_vec) {
+                // Scales of four K blocks per load (16 bytes per row): a quarter of the load instructions and of
+                // the sectors touched (a token's scales of eight consecutive K blocks share one 32-byte sector, and
+                // the 32 lanes of a warp read 32 different rows).  The next group is loaded before the current one
+                // is used.  Needs ceil(K/128) % 4 == 0 and 16-byte aligned scale rows; the host checks.
+                float4 sa_c = ldg4_in_place(p.sa + sa_off), sw_c[SPLIT];
+#pragma unroll
+                for (int h = 0; h < SPLIT; ++h) sw_c[h] = ldg4_in_place(p.sw + sw_off[h]);
+                for (int kb = 0; kb < num_kb && ok; kb += 4) {
+                    float4 sa_n = sa_c, sw_n[SPLIT];
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) sw_n[h] = sw_c[h];
+                    if (kb + 4 < num_kb) {
+                        sa_n = ldg4_in_place(p.sa + (sa_off + kb + 4));
+#pragma unroll
+                        for (int h = 0; h < SPLIT; ++h) sw_n[h] = ldg4_in_place(p.sw + (sw_off[h] + kb + 4));
+                    }
+                    float t[SPLIT];
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_c.x, sw_c[h].x);
+                    ok = k_block(t);
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_c.y, sw_c[h].y);
+                    ok = ok && k_block(t);
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_c.z, sw_c[h].z);
+                    ok = ok && k_block(t);
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_c.w, sw_c[h].w);
+                    ok = ok && k_block(t);
+                    sa_c = sa_n;
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) sw_c[h] = sw_n[h];
                 }
-                if (kb + 1 < num_kb && !k_block(kb + 1, 1)) {
-                    ok = false;
-                    break;
+            } else {
+                // Scales are loaded two K blocks before their use (an L2 hit takes about one K block); the two
+                // register sets alternate statically through the unrolled loop below.
+                float sa_q[2], sw_q[2][SPLIT];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    sa_q[j] = 0.0f;
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) sw_q[j][h] = 0.0f;
+                    if (j < num_kb) {
+                        sa_q[j] = ldg_in_place(p.sa + (sa_off + j));
+#pragma unroll
+                        for (int h = 0; h < SPLIT; ++h) sw_q[j][h] = ldg_in_place(p.sw + (sw_off[h] + j));
+                    }
+                }
+                auto k_block_scalar = [&](int kb, int j) -> bool {
+                    float t[SPLIT];
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_q[j], sw_q[j][h]);
+                    if (kb + 2 < num_kb) {
+                        sa_q[j] = ldg_in_place(p.sa + (sa_off + kb + 2));
+#pragma unroll
+                        for (int h = 0; h < SPLIT; ++h) sw_q[j][h] = ldg_in_place(p.sw + (sw_off[h] + kb + 2));
+                    }
+                    return k_block(t);
+                };
+                for (int kb = 0; kb < num_kb && ok; kb += 2) {
+                    ok = k_block_scalar(kb, 0);
+                    if (ok && kb + 1 < num_kb) ok = k_block_scalar(kb + 1, 1);
                 }
             }
             if (!ok) break;

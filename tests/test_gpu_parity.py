@@ -239,7 +239,7 @@ def bw_knobs(g, monkeypatch):
 @pytest.mark.parametrize("issuers", [1, 2])
 @pytest.mark.parametrize("variant", ["dense_bn64", "dense_bn128", "dense_bn256", "pair", None])
 def test_blockwise_edge_shapes(g, oracle, variant, issuers, bw_knobs):
-    bw_knobs(1, issuers)
+    bw_knobs(issuers, issuers)   # (1, 1): N = 256 MMAs, one issuer; (2, 2): column halves, one issuer per half
     g.force_variant(variant)
     gen = torch.Generator().manual_seed(51)
     shapes = [(1, 8, 16), (7, 120, 128), (33, 136, 144), (128, 128, 128), (129, 264, 400), (257, 1000, 1040),
