@@ -35,6 +35,7 @@ _libdef.define("int8_matmul(Tensor A, Tensor B, float alpha) -> Tensor")
 _libdef.define("int8_matmul_i32(Tensor A, Tensor B) -> Tensor")
 _libdef.define("int8_matmul_scaled(Tensor A, Tensor B, Tensor a_scale, Tensor b_scale) -> Tensor")
 _libdef.define("int8_matmul_blockwise(Tensor A, Tensor B, Tensor A_scale, Tensor B_scale) -> Tensor")
+_libdef.define("int8_matmul_blockwise_f32(Tensor A, Tensor B, Tensor A_scale, Tensor B_scale) -> Tensor")
 _libdef.define("quantize_token_block(Tensor a) -> (Tensor, Tensor)")
 _libdef.define("quantize_token(Tensor a) -> (Tensor, Tensor)")
 _libdef.define("hadamard_quantize_token_block(Tensor a, int block) -> (Tensor, Tensor)")
@@ -151,8 +152,9 @@ def _int8_matmul_scaled_cuda(A: torch.Tensor, B: torch.Tensor, a_scale: torch.Te
     return out
 
 
-def _int8_matmul_blockwise_cuda(A: torch.Tensor, B: torch.Tensor, A_scale: torch.Tensor, B_scale: torch.Tensor) -> torch.Tensor:
-    name = "int8_matmul_blockwise"
+def _int8_matmul_blockwise_cuda(A: torch.Tensor, B: torch.Tensor, A_scale: torch.Tensor, B_scale: torch.Tensor,
+                                f32: bool = False) -> torch.Tensor:
+    name = "int8_matmul_blockwise_f32" if f32 else "int8_matmul_blockwise"
     M, N, K = _check_operands(name, A, B)
     KB, NB = -(-K // KBLOCK), -(-N // KBLOCK)
     _check_scale(name, "A_scale", A_scale, (M, KB), A.device)
@@ -167,10 +169,10 @@ def _int8_matmul_blockwise_cuda(A: torch.Tensor, B: torch.Tensor, A_scale: torch
         A_scale, ld_sa = A_scale.contiguous(), KB
     if ld_sw < KB:
         B_scale, ld_sw = B_scale.contiguous(), KB
-    out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    out = torch.empty((M, N), dtype=torch.float32 if f32 else torch.bfloat16, device=A.device)
+    fn = _C.gi8_matmul_blockwise_f32 if f32 else _C.gi8_matmul_blockwise
     with _on_device(A.device):
-        rc = _C.gi8_matmul_blockwise(_ptr(A), _ptr(B), _ptr(A_scale), ld_sa, _ptr(B_scale), ld_sw, _ptr(out),
-                                     M, N, K, _stream_ptr(A.device))
+        rc = fn(_ptr(A), _ptr(B), _ptr(A_scale), ld_sa, _ptr(B_scale), ld_sw, _ptr(out), M, N, K, _stream_ptr(A.device))
     _lib.check(_C, rc)
     return out
 
@@ -179,6 +181,7 @@ _libdef.impl("int8_matmul", _int8_matmul_cuda, "CUDA")
 _libdef.impl("int8_matmul_i32", _int8_matmul_i32_cuda, "CUDA")
 _libdef.impl("int8_matmul_scaled", _int8_matmul_scaled_cuda, "CUDA")
 _libdef.impl("int8_matmul_blockwise", _int8_matmul_blockwise_cuda, "CUDA")
+_libdef.impl("int8_matmul_blockwise_f32", lambda A, B, sa, sw: _int8_matmul_blockwise_cuda(A, B, sa, sw, True), "CUDA")
 
 
 # --------------------------------------------------------------------------------------------------
@@ -221,6 +224,14 @@ def _(x: torch.Tensor, y: torch.Tensor, A_scale: torch.Tensor, B_scale: torch.Te
     return torch.empty(x.shape[0], y.shape[0], device=x.device, dtype=torch.bfloat16)
 
 
+@torch.library.register_fake(f"{_NS}::int8_matmul_blockwise_f32")
+def _(x: torch.Tensor, y: torch.Tensor, A_scale: torch.Tensor, B_scale: torch.Tensor):
+    _fake_common(x, y)
+    torch._check(A_scale.dtype == torch.float32 and B_scale.dtype == torch.float32, lambda: "scales must be float32")
+    torch._check(len(A_scale.shape) == 2 and len(B_scale.shape) == 2, lambda: "scales must be 2D tensors")
+    return torch.empty(x.shape[0], y.shape[0], device=x.device, dtype=torch.float32)
+
+
 # --------------------------------------------------------------------------------------------------
 # public functions
 # --------------------------------------------------------------------------------------------------
@@ -260,6 +271,26 @@ def matmul_blockwise(x_q: torch.Tensor, w_q: torch.Tensor, x_scale: torch.Tensor
     x_q (M, K) int8, w_q (N, K) int8, x_scale (M, ceil(K/128)) fp32, w_scale (ceil(N/128), ceil(K/128)) fp32.
     """
     return torch.ops.gemm_int8_CUDA.int8_matmul_blockwise(x_q, w_q, x_scale, w_scale)
+
+
+def matmul_blockwise_f32(x_q: torch.Tensor, w_q: torch.Tensor, x_scale: torch.Tensor, w_scale: torch.Tensor) -> torch.Tensor:
+    """`matmul_blockwise` before its bf16 cast: the fp32 accumulators (one fused multiply-add per 128-wide K block,
+    ascending).  The partial result of a K-sharded GEMM (see `dist.matmul_blockwise_ksharded`)."""
+    return torch.ops.gemm_int8_CUDA.int8_matmul_blockwise_f32(x_q, w_q, x_scale, w_scale)
+
+
+def sum_parts_bf16(parts: torch.Tensor) -> torch.Tensor:
+    """parts fp32 [P, ...] (contiguous) -> bf16 [...]: ((parts[0] + parts[1]) + parts[2]) + ... in fp32, cast once."""
+    if not parts.is_cuda or parts.dtype != torch.float32 or parts.dim() < 2:
+        raise RuntimeError("sum_parts_bf16: a CUDA float32 tensor [P, ...] is expected")
+    parts = parts.contiguous()
+    P = parts.shape[0]
+    count = parts[0].numel()
+    out = torch.empty(parts.shape[1:], dtype=torch.bfloat16, device=parts.device)
+    with _on_device(parts.device):
+        rc = _C.gi8_sum_parts_bf16(_ptr(parts), P, count, _ptr(out), count, _stream_ptr(parts.device))
+    _lib.check(_C, rc)
+    return out
 
 
 def _quantize(a: torch.Tensor, per_block: bool):
@@ -396,5 +427,6 @@ if _os.environ.get("GEMM_INT8_KERNEL"):
 
 from .linear import Int8Linear  # noqa: E402
 
-__all__ = ["matmul", "matmul_i32", "matmul_scaled", "matmul_blockwise", "quantize_per_token_block",
+__all__ = ["matmul", "matmul_i32", "matmul_scaled", "matmul_blockwise", "matmul_blockwise_f32", "sum_parts_bf16",
+           "quantize_per_token_block",
            "quantize_per_token", "Int8Linear", "force_variant", "pick_variant", "device_status", "check_device", "reload_env"]

@@ -537,6 +537,32 @@ __global__ void wait_timeout_selftest_kernel(uint32_t* status)
     __syncthreads();
 }
 
+// out[i] = bf16( ((parts[0][i] + parts[1][i]) + parts[2][i]) + ... ): the partial accumulators of a K-sharded GEMM
+// summed in the order of the parts (fp32, round to nearest each step) and cast once.  HBM-bound: n_parts * 4 + 2
+// bytes per element, 16-byte loads, grid-stride over a grid of 16 CTAs per SM.
+template <bool VEC>
+__global__ void sum_parts_bf16_kernel(const float* __restrict__ parts, int n_parts, int64_t part_stride,
+                                      uint16_t* __restrict__ out, int64_t count)
+{
+    const int64_t step = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    if constexpr (VEC) {
+        for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < count / 4; i += step) {
+            float4 a = *reinterpret_cast<const float4*>(parts + 4 * i);
+            for (int r = 1; r < n_parts; ++r) {
+                const float4 b = *reinterpret_cast<const float4*>(parts + r * part_stride + 4 * i);
+                a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+            }
+            *reinterpret_cast<uint2*>(out + 4 * i) = make_uint2(gi8::pack_bf16x2(a.x, a.y), gi8::pack_bf16x2(a.z, a.w));
+        }
+    } else {
+        for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < count; i += step) {
+            float a = parts[i];
+            for (int r = 1; r < n_parts; ++r) a += parts[r * part_stride + i];
+            out[i] = gi8::to_bf16_bits(a);
+        }
+    }
+}
+
 template <typename T>
 static int launch_hadamard_quant(const T* in, int8_t* q, float* scales, int64_t M, int K, int KB, int H, cudaStream_t s)
 {
@@ -854,15 +880,15 @@ int gi8_quantize_token(const void* in, int in_dtype, int8_t* q, float* scales, i
 // peer's, the latter through mapped peer memory) instead of `out`.
 static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw, int64_t ld_sw,
                           void* out, int64_t M, int64_t N, int64_t K, void* stream, void* const* gather, int n_out,
-                          int64_t n_total, int64_t col0)
+                          int64_t n_total, int64_t col0, bool out_f32 = false)
 {
     if (gather) out = gather[0];
-    if (int rc = check_common(x, y, out, M, N, K, 2)) return rc;
+    if (int rc = check_common(x, y, out, M, N, K, out_f32 ? 4 : 2)) return rc;
     if (M == 0 || N == 0) return GI8_OK;
     DeviceState* st;
     if (int rc = get_device_state(&st)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (K == 0) return zero_output(out, M * N * 2, s);
+    if (K == 0) return zero_output(out, M * N * (out_f32 ? 4 : 2), s);
     const int64_t KB = (K + kBK - 1) / kBK;
     if (!sa || !sw) return fail(GI8_ERR_INVALID_ARGUMENT, "null scale pointer");
     if (ld_sa < KB || ld_sw < KB)
@@ -877,6 +903,7 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     p.out = out, p.sa = sa, p.sw = sw, p.status = st->status, p.ldo = N, p.ld_sa = ld_sa, p.ld_sw = ld_sw;
     p.M = (int)M, p.N = (int)N, p.K = (int)K;
     p.vec_ok = (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (N % 8 == 0);
+    p.out_f32 = out_f32 ? 1 : 0;
     p.n_out = 1, p.out_col0 = 0;
     p.scale_vec = (KB % 4 == 0) && (ld_sa % 4 == 0) && (ld_sw % 4 == 0) && reinterpret_cast<uintptr_t>(sa) % 16 == 0 &&
                   reinterpret_cast<uintptr_t>(sw) % 16 == 0;
@@ -914,7 +941,7 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
             if (int rc = make_output_map(&mo.m[i], gather[i], M, n_total, n_total, box_cols)) return rc;
         p.tma_store = 1, p.n_out = n_out, p.out_col0 = static_cast<int>(col0);
     } else {
-        p.tma_store = p.vec_ok && knobs().tma_store;
+        p.tma_store = p.vec_ok && knobs().tma_store && !out_f32;  // the fp32 form stores from registers
         if (p.tma_store)
             if (int rc = make_output_map(&mo.m[0], out, M, N, N, box_cols)) return rc;
     }
@@ -962,6 +989,38 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
                          int64_t ld_sw, void* out, int64_t M, int64_t N, int64_t K, void* stream)
 {
     return blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, out, M, N, K, stream, nullptr, 1, N, 0);
+}
+
+int gi8_matmul_blockwise_f32(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                             int64_t ld_sw, float* out, int64_t M, int64_t N, int64_t K, void* stream)
+{
+    return blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, out, M, N, K, stream, nullptr, 1, N, 0, true);
+}
+
+int gi8_sum_parts_bf16(const float* parts, int n_parts, int64_t part_stride, void* out_bf16, int64_t count, void* stream)
+{
+    if (n_parts < 1 || n_parts > 64 || count < 0 || part_stride < count)
+        return fail(GI8_ERR_INVALID_ARGUMENT, "n_parts must be in [1, 64] and part_stride at least count");
+    if (count == 0) return GI8_OK;
+    if (!parts || !out_bf16) return fail(GI8_ERR_INVALID_ARGUMENT, "null pointer");
+    if (reinterpret_cast<uintptr_t>(parts) % 4 || reinterpret_cast<uintptr_t>(out_bf16) % 2)
+        return fail(GI8_ERR_MISALIGNED, "parts must be 4-byte and out 2-byte aligned");
+    DeviceState* st;
+    if (int rc = get_device_state(&st)) return rc;
+    const bool vec = reinterpret_cast<uintptr_t>(parts) % 16 == 0 && reinterpret_cast<uintptr_t>(out_bf16) % 8 == 0 &&
+                     part_stride % 4 == 0 && count % 4 == 0;
+    const int64_t items = vec ? count / 4 : count;
+    int64_t blocks = (items + 255) / 256;
+    const int64_t cap = static_cast<int64_t>(st->sm_count) * 16;
+    if (blocks > cap) blocks = cap;
+    if (vec)
+        sum_parts_bf16_kernel<true><<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            parts, n_parts, part_stride, static_cast<uint16_t*>(out_bf16), count);
+    else
+        sum_parts_bf16_kernel<false><<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+            parts, n_parts, part_stride, static_cast<uint16_t*>(out_bf16), count);
+    GI8_CUDA(cudaGetLastError());
+    return GI8_OK;
 }
 
 int gi8_matmul_blockwise_allgather(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,

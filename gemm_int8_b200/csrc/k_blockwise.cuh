@@ -71,6 +71,8 @@ struct BlockwiseParams {
                     // N-sharded group: each rank's full [M, N_total] matrix, peers through mapped peer memory)
     int out_col0;   // column of this GEMM's first output column in those matrices
     int scale_vec;  // ceil(K/128) % 4 == 0 and the rows of sa and sw are 16-byte aligned: scales are loaded four at a time
+    int out_f32;    // store the fp32 accumulators themselves (out is float [M,N]) instead of their bf16 cast; the
+                    // partial results of a K-sharded GEMM, and the bit-exact check of the accumulation order
 };
 
 constexpr int kMaxOutputs = 8;
@@ -588,6 +590,29 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                                              "r"(stg), "r"(p.out_col0 + col0), "r"(row0)
                                              : "memory");
                             tma_store_commit();
+                        }
+                    }
+                }
+            } else if (p.out_f32) {
+                if (row_ok) {
+#pragma unroll
+                    for (int h = 0; h < SPLIT; ++h) {
+                        const int c0 = col_base + h * kSegStrideH;
+                        if (c0 >= p.N) continue;
+                        float* dst = static_cast<float*>(p.out) + static_cast<int64_t>(row) * p.ldo + c0;
+                        const uint64_t* a = acc + h * (SEGW / 2);
+                        if (c0 + SEGW <= p.N && p.vec_ok) {
+#pragma unroll
+                            for (int j = 0; j < SEGW / 2; j += 2)
+                                *reinterpret_cast<ulonglong2*>(dst + 2 * j) = make_ulonglong2(a[j], a[j + 1]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < SEGW / 2; ++j) {
+                                float lo, hi;
+                                unpack_f32x2(a[j], lo, hi);
+                                if (c0 + 2 * j < p.N) dst[2 * j] = lo;
+                                if (c0 + 2 * j + 1 < p.N) dst[2 * j + 1] = hi;
+                            }
                         }
                     }
                 }

@@ -102,6 +102,45 @@ def matmul_blockwise_nsharded(x_q: torch.Tensor, w_q_shard: torch.Tensor, x_scal
     return all_gather_ragged(local, N, group=group)
 
 
+def kshard_bounds(K: int, world: int, rank: int, block: int = KBLOCK) -> tuple[int, int]:
+    """Columns [k0, k1) of x and of the weight owned by `rank` in a K-sharded (row-parallel) layer: whole 128-wide
+    K blocks, as even as possible, so that no scale block is split."""
+    return shard_bounds(K, world, rank, block)
+
+
+def matmul_blockwise_ksharded(x_q_shard: torch.Tensor, w_q_shard: torch.Tensor, x_scale_shard: torch.Tensor,
+                              w_scale_shard: torch.Tensor, group=None, compute: Optional[Callable] = None,
+                              reduce: Optional[Callable] = None) -> torch.Tensor:
+    """Blockwise W8A8 GEMM with K sharded over the ranks (a row-parallel layer), reduce-scattered over token rows.
+
+    Rank r passes its K slice of everything: ``x_q[:, k0:k1]``, ``w_q[:, k0:k1]`` and the matching columns of both
+    scale arrays (see `kshard_bounds`).  Every rank computes the fp32 accumulators of its slice for the whole
+    ``[M, N]`` output (one fused multiply-add per K block, ascending, as the unsharded kernel does), the ranks
+    exchange row blocks with one all-to-all (rank j receives rows ``[j M/g, (j+1) M/g)`` of every rank's partial:
+    the bytes of a reduce-scatter), and each rank adds the g partials of its rows IN RANK ORDER and casts to bf16.
+    The result therefore is ``bf16(((acc_0 + acc_1) + acc_2) + ...)`` with acc_r the chain over rank r's K blocks --
+    a fixed order, which a CPU restatement reproduces bit for bit; it is not the unsharded kernel's single chain
+    (the difference is fp32 rounding of g - 1 additions).  M must be a multiple of the world size.
+    Returns this rank's bf16 ``[M / g, N]`` rows.
+    `compute` / `reduce` replace the local GEMM and the ordered sum (tests inject CPU checkers there).
+    """
+    if compute is None:
+        from . import matmul_blockwise_f32 as compute
+    if reduce is None:
+        from . import sum_parts_bf16 as reduce
+    world = dist.get_world_size(group)
+    part = compute(x_q_shard, w_q_shard, x_scale_shard, w_scale_shard)  # fp32 [M, N]
+    M, N = part.shape
+    if M % world:
+        raise ValueError(f"M={M} must be a multiple of the world size {world}")
+    if world == 1:
+        return reduce(part.reshape(1, M, N))
+    recv = torch.empty((world, M // world, N), dtype=part.dtype, device=part.device)
+    # send buffer viewed as [world, M/world, N]: block j goes to rank j; received block r came from rank r
+    dist.all_to_all_single(recv.view(-1), part.contiguous().view(-1), group=group)
+    return reduce(recv)
+
+
 class FusedGatherGemm:
     """N-sharded blockwise GEMM whose epilogue writes every output block straight into every rank's full
     [M, N] matrix (TMA stores through mapped peer memory), so the all-gather rides on the GEMM tile by tile and no

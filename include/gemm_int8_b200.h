@@ -113,6 +113,23 @@ int gi8_matmul_scaled_static(const int8_t* x, const int8_t* y, const float* sx, 
                              int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * gi8_matmul_blockwise with the fp32 accumulators themselves as the result (out_f32 float [M,N] row-major, 4-byte
+ * aligned): the value gi8_matmul_blockwise would round to bf16.  No reference counterpart (the reference's epilogue
+ * always casts, csrc/kernels/gemm.cu:59-63).  Two uses: the bit-exact check of the accumulation order, and the
+ * partial result of a K-sharded (row-parallel) GEMM, whose per-rank partials are summed across ranks before the cast.
+ */
+int gi8_matmul_blockwise_f32(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                             int64_t ld_sw, float* out_f32, int64_t M, int64_t N, int64_t K, void* stream);
+
+/*
+ * out[i] = bf16( ((parts[0][i] + parts[1][i]) + parts[2][i]) + ... ) for i < count, parts[r] = parts + r * part_stride:
+ * the second step of a K-sharded GEMM -- the ranks' fp32 partials of one output slice, summed in the order given
+ * (so the result does not depend on which rank finished first) and cast once.  No reference counterpart.
+ * n_parts <= 64.
+ */
+int gi8_sum_parts_bf16(const float* parts, int n_parts, int64_t part_stride, void* out_bf16, int64_t count, void* stream);
+
+/*
  * N-sharded form of gi8_matmul_blockwise with the all-gather fused into the epilogue (no reference counterpart; the
  * reference is single-GPU).  This rank holds rows [col0, col0 + N) of the weight (y [N,K], sw [ceil(N/128), ...]) and
  * computes columns [col0, col0 + N) of the full [M, n_total] result; every output block (32 rows x 64 columns, or

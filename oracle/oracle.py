@@ -144,6 +144,31 @@ def c_matmul_blockwise(x, y, sa, sw, return_acc=False):
     return (out, acc) if return_acc else out
 
 
+def c_matmul_blockwise_ksharded(x, y, sa, sw, world, block=KBLOCK):
+    """Restatement of the K-sharded (row-parallel) blockwise GEMM: the K blocks are dealt to `world` ranks in whole
+    blocks (as evenly as possible, leading ranks one more), each rank's fp32 accumulator is the ascending
+    fused-multiply-add chain over ITS blocks, the rank accumulators are added in rank order in fp32
+    (round to nearest each step) and the sum is rounded to bf16.  Returns uint16 bit patterns [M, N]."""
+    x, y = _np(x, np.int8), _np(y, np.int8)
+    sa, sw = _np(sa, np.float32), _np(sw, np.float32)
+    K = x.shape[1]
+    nb = -(-K // block)
+    base, extra = divmod(nb, world)
+    total = None
+    for r in range(world):
+        b0 = r * base + min(r, extra)
+        b1 = b0 + base + (1 if r < extra else 0)
+        k0, k1 = min(b0 * block, K), min(b1 * block, K)
+        if k1 == k0:
+            acc = np.zeros((x.shape[0], y.shape[0]), np.float32)
+        else:
+            _, acc = c_matmul_blockwise(np.ascontiguousarray(x[:, k0:k1]), np.ascontiguousarray(y[:, k0:k1]),
+                                        np.ascontiguousarray(sa[:, b0:b1]), np.ascontiguousarray(sw[:, b0:b1]),
+                                        return_acc=True)
+        total = acc if total is None else (total + acc).astype(np.float32)
+    return np_bf16_rne(total)
+
+
 def c_quantize_blocks(v, rb, cb):
     v = _np(v, np.float32)
     R, C = v.shape

@@ -60,11 +60,55 @@ def _worker(rank, world, port, N, fail_rank, q):
             pass
 
 
-def _run(world, N, fail_rank=-1):
+def _kshard_worker(rank, world, port, N, fail_rank, q):
+    """K-sharded (row-parallel) form: every rank holds a K slice; the ranks' fp32 partials are exchanged with one
+    all-to-all and added in rank order.  The local GEMM and the ordered sum are the CPU oracle's."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import datetime
+
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    try:
+        from gemm_int8_b200 import dist as gdist, workloads
+        from oracle import oracle as O
+
+        M, K = 12 * world, 640   # five K blocks: ragged over 2 and 3 ranks
+        x, y, sa, sw = workloads.nshard(M, N, K, seed=78)
+        k0, k1 = gdist.kshard_bounds(K, world, rank)
+        xs, ys = x[:, k0:k1].contiguous(), y[:, k0:k1].contiguous()
+        sas, sws = sa[:, k0 // 128: -(-k1 // 128)].contiguous(), sw[:, k0 // 128: -(-k1 // 128)].contiguous()
+
+        def compute(a, b, c, d):
+            return torch.from_numpy(O.c_matmul_blockwise(a, b, c, d, return_acc=True)[1])
+
+        def reduce(parts):
+            tot = parts[0].numpy().copy()
+            for r in range(1, parts.shape[0]):
+                tot = (tot + parts[r].numpy()).astype(np.float32)
+            return O.to_torch_bf16(O.np_bf16_rne(tot))
+
+        rows = gdist.matmul_blockwise_ksharded(xs, ys, sas, sws, compute=compute, reduce=reduce)
+        ref = O.c_matmul_blockwise_ksharded(x, y, sa, sw, world)
+        m = M // world
+        ok = rows.shape == (m, N) and np.array_equal(O.bf16_bits(rows), ref[rank * m:(rank + 1) * m])
+        # and the sharded result stays within one bf16 ulp (plus the fp32 re-association floor) of the unsharded chain
+        one = O.c_matmul_blockwise(x, y, sa, sw)[rank * m:(rank + 1) * m]
+        ok = ok and int(O.bf16_ulp_distance(O.bf16_bits(rows), one).max()) <= 1
+        q.put((rank, "ok" if ok else "mismatch"))
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, f"error: {type(e).__name__}: {e}"))
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def _run(world, N, fail_rank=-1, worker=None):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, N, fail_rank, q)) for r in range(world)]
+    procs = [ctx.Process(target=worker or _worker, args=(r, world, port, N, fail_rank, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = dict(q.get(timeout=120) for _ in range(world))
@@ -113,3 +157,8 @@ def test_rank_failure_before_collective_is_reported_not_hung():
     res = _run(2, 512, fail_rank=1)
     assert res[1].startswith("error: RuntimeError: injected")
     assert res[0].startswith("error")
+
+
+def test_kshard_reduce_scatter_world2_and_3():
+    assert _run(2, 264, worker=_kshard_worker) == {0: "ok", 1: "ok"}
+    assert _run(3, 136, worker=_kshard_worker) == {0: "ok", 1: "ok", 2: "ok"}

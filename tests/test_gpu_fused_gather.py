@@ -1,4 +1,5 @@
-"""Fused GEMM + all-gather across GPUs: needs at least two GPUs on the box; skipped otherwise."""
+"""Fused GEMM + all-gather and the K-sharded reduce-scatter across GPUs: needs at least two GPUs on the box;
+skipped otherwise."""
 import os
 import subprocess
 import sys
@@ -19,3 +20,4 @@ def test_fused_gather_matches_unsharded_kernel_on_two_gpus():
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert res.stdout.count("bit-equal to the unsharded kernel = True") == 4, res.stdout[-3000:]
+    assert res.stdout.count("bit-equal to the single-GPU sum = True") == 2, res.stdout[-3000:]

@@ -299,6 +299,45 @@ def test_blockwise_strided_scales(g, oracle):
     assert_bits_equal(oracle, out, oracle.c_matmul_blockwise(x, y, sa.contiguous(), sw.contiguous()), "strided scales")
 
 
+def test_blockwise_f32_accumulators_and_ksharded_sum(g, oracle):
+    """The fp32-result entry point returns the oracle's accumulators bit for bit (every tile width, ragged shapes),
+    and the K-sharded form -- per-slice accumulators added in slice order, then cast -- equals the oracle's
+    restatement of it, emulated on one GPU for 2, 3 and 4 slices."""
+    gen = torch.Generator().manual_seed(53)
+    for variant in (None, "dense_bn256", "dense_bn128", "dense_bn64", "pair"):
+        g.force_variant(variant)
+        for (M, N, K) in [(7, 120, 128), (129, 264, 400), (300, 1000, 2048)]:
+            KB, NB = -(-K // 128), -(-N // 128)
+            x, y = rand_i8((M, K), M + 5), rand_i8((N, K), N + 5)
+            sa = torch.rand(M, KB, generator=gen) * 0.02 + 1e-3
+            sw = torch.rand(NB, KB, generator=gen) * 0.02 + 1e-3
+            acc = g.matmul_blockwise_f32(x.cuda(), y.cuda(), sa.cuda(), sw.cuda())
+            assert acc.dtype == torch.float32
+            _, ref_acc = oracle.c_matmul_blockwise(x, y, sa, sw, return_acc=True)
+            assert np.array_equal(acc.cpu().numpy().view(np.uint32), ref_acc.view(np.uint32)), (variant, M, N, K)
+    g.force_variant(None)
+    M, N, K = 96, 520, 2048 + 128
+    KB, NB = K // 128, -(-N // 128)
+    x, y = rand_i8((M, K), 71), rand_i8((N, K), 72)
+    sa = torch.rand(M, KB, generator=gen) * 0.02 + 1e-3
+    sw = torch.rand(NB, KB, generator=gen) * 0.02 + 1e-3
+    from gemm_int8_b200 import dist as gdist
+
+    for world in (2, 3, 4):
+        parts = []
+        for r in range(world):
+            k0, k1 = gdist.kshard_bounds(K, world, r)
+            parts.append(g.matmul_blockwise_f32(x[:, k0:k1].contiguous().cuda(), y[:, k0:k1].contiguous().cuda(),
+                                                sa[:, k0 // 128:k1 // 128].contiguous().cuda(),
+                                                sw[:, k0 // 128:k1 // 128].contiguous().cuda()))
+        out = g.sum_parts_bf16(torch.stack(parts))
+        assert_bits_equal(oracle, out, oracle.c_matmul_blockwise_ksharded(x, y, sa, sw, world), f"k-sharded world {world}")
+    # the unaligned (scalar) form of the sum kernel
+    odd = torch.stack([p[:, :519].contiguous() for p in parts])
+    ref = oracle.c_matmul_blockwise_ksharded(x, y, sa, sw, 4)[:, :519]
+    assert_bits_equal(oracle, g.sum_parts_bf16(odd), ref, "k-sharded, odd width")
+
+
 def test_config2_blockwise_prefill_full_size(g, oracle):
     from gemm_int8_b200 import workloads
 
