@@ -5,10 +5,11 @@
 # recompiled for Blackwell: the same-box comparator of the dense GEMM and the pin of the CPU oracle.
 # Nothing is copied into the repository; baseline/_ref/ is ignored by git.
 #
-# usage: baseline/build_reference.sh [path of the reference checkout]   (takes about five minutes)
+# usage: baseline/build_reference.sh [path of the reference checkout]   (takes about three minutes)
+# Without an argument: $GEMM_INT8_REFERENCE, else a checkout named "reference" beside this repository.
 set -euo pipefail
-REF=${1:-${GEMM_INT8_REFERENCE:-/root/reference}}
 HERE=$(cd "$(dirname "$0")" && pwd)
+REF=${1:-${GEMM_INT8_REFERENCE:-$HERE/../../reference}}
 OUT=$HERE/_ref
 SRC=$REF/csrc/kernels
 [ -f "$SRC/gemm.cu" ] || { echo "reference sources not found under $REF" >&2; exit 2; }
