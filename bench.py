@@ -49,7 +49,7 @@ NOMINAL_INT8_TOPS = 4500.0
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under
 # profiles/: keyed by (workload, M, N, K).  Other shapes report null.
 NCU_TRAFFIC = {
-    ("blockwise_prefill", 2048, 11008, 4096): (64.3e6, "profiles/blockwise_gemm_kernel__blockwise_prefill_2048x11008x4096.md"),
+    ("blockwise_prefill", 2048, 11008, 4096): (67.1e6, "profiles/blockwise_gemm_kernel__blockwise_prefill_2048x11008x4096.md"),
     ("square8192", 8192, 8192, 8192): (444.3e6, "profiles/dense_gemm_kernel__square8192.md"),
     ("decode", 16, 14336, 4096): (58.97e6, "profiles/smallm_cluster_kernel__decode_16x14336x4096.md"),
 }
