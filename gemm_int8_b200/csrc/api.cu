@@ -66,6 +66,9 @@ struct Knobs {
     int splits = 0;
     int bw_halves = 2;
     int bw_issuers = 0;  // 0: one for the 256-wide tile, two for the narrower ones
+    // The caller promises that the weight operand of the small-M path is not written by the kernel that precedes the
+    // call in its stream (weights quantised ahead of time): its first tiles are then requested before that kernel ends.
+    bool static_weights = false;
 };
 Knobs g_knobs;
 std::once_flag g_knobs_once;
@@ -82,6 +85,7 @@ void load_knobs()
     if (const char* e = getenv("GEMM_INT8_SPLITS")) k.splits = atoi(e);
     if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 1 ? 1 : 2;
     if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 2 ? 2 : atoi(e) == 1 ? 1 : 0;
+    if (const char* e = getenv("GEMM_INT8_STATIC_WEIGHTS")) k.static_weights = e[0] == '1';
     g_knobs = k;
 }
 
@@ -717,6 +721,7 @@ int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const f
             SmallMParams q{};
             q.out = out, q.sx = sx, q.sw = sw, q.status = st->status, q.ldo = N;
             q.M = (int)M, q.N = (int)N, q.K = (int)K, q.kb_per_split = pl.kb_per_split, q.splits = pl.splits;
+            q.static_w = knobs().static_weights && knobs().pdl;
             switch (pl.mt) {
                 case 16: return launch_smallm_cluster<16, 6>(st, 28, x, y, q, pl, s);
                 case 32: return launch_smallm_cluster<32, 5>(st, 29, x, y, q, pl, s);

@@ -34,6 +34,7 @@ struct SmallMParams {
     int M, N, K;
     int kb_per_split;   // K blocks (of 128) per split
     int splits;
+    int static_w;       // weights are not written by the preceding kernel: their first tiles may be fetched before it ends
 };
 
 template <int MT, int STAGES>
@@ -296,15 +297,24 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
         prefetch_tensormap(&map_w);
         prefetch_tensormap(&map_x);
         pdl_launch_dependents();  // the next kernel may be scheduled as soon as SMs free up
-        pdl_wait();               // everything above overlapped the previous kernel's tail; global reads start here
         const uint64_t pol_w = l2_policy_evict_first();
         const uint64_t pol_x = l2_policy_evict_last();
         const int first = min(num_kb, STAGES);
+        // Everything above overlapped the previous kernel's tail.  Reads of what that kernel may have written start
+        // after the dependency wait; the weights, when the caller declared them static, are requested before it, so
+        // that the first tiles are already on their way when the previous kernel ends.
+        if (!p.static_w) pdl_wait();
         for (int i = 0; i < first; ++i) {
             uint8_t* sw_tile = smem + i * kStageBytes;
             mbar_arrive_expect_tx(&bar_full[i], kBytesW + kBytesX);
             tma_load_2d_hint(sw_tile, &map_w, &bar_full[i], (kb_begin + i * kb_step) * kBK, tile_n * kSmallMTileN, pol_w);
-            tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[i], (kb_begin + i * kb_step) * kBK, 0, pol_x);
+            if (!p.static_w)
+                tma_load_2d_hint(sw_tile + kBytesW, &map_x, &bar_full[i], (kb_begin + i * kb_step) * kBK, 0, pol_x);
+        }
+        if (p.static_w) {
+            pdl_wait();
+            for (int i = 0; i < first; ++i)
+                tma_load_2d_hint(smem + i * kStageBytes + kBytesW, &map_x, &bar_full[i], (kb_begin + i * kb_step) * kBK, 0, pol_x);
         }
     }
     if (warp == 1) {

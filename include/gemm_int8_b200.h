@@ -220,6 +220,10 @@ int gi8_selftest_wait_timeout(void* stream);
 /*
  * The GEMM_INT8_* tuning variables (tile band height, TMA-store epilogue, programmatic dependent launch, K splits,
  * blockwise MMA shape and issuer count) are read once, when the library is first used; this reads them again.
+ * GEMM_INT8_STATIC_WEIGHTS=1 (default 0) is a promise rather than a tuning: the weight operand of gi8_matmul_scaled's
+ * small-M path is not written by the work that directly precedes the call in its stream (weights quantised ahead of
+ * time), so the kernel may request its first weight tiles while that work is still finishing.  Activations, scales
+ * and the output are touched only after it has ended, whatever the setting.
  * No reference counterpart (its tuning is compile-time, CMakeLists.txt:49-51).
  */
 int gi8_reload_env(void);

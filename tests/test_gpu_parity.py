@@ -188,6 +188,35 @@ def test_config3_decode_shapes(g, oracle, K, N):
         g.force_variant(None)
 
 
+def test_smallm_static_weights_option(g, oracle, monkeypatch):
+    """GEMM_INT8_STATIC_WEIGHTS=1 lets the small-M kernel request its first weight tiles before the preceding
+    kernel has ended; activations and scales are still read after it.  Here the activations of every call are
+    written by a kernel directly before it (a device copy), back to back, and the bits must stay the oracle's."""
+    from gemm_int8_b200 import workloads
+
+    monkeypatch.setenv("GEMM_INT8_STATIC_WEIGHTS", "1")
+    g.reload_env()
+    try:
+        for (M, N, K) in [(16, 4096, 4096), (3, 1000, 1040), (64, 14336, 4096)]:
+            xq, wq, sx, sw = workloads.decode(M, N, K)
+            cases = [(xq, wq, sx, sw)]
+            for i in range(3):   # further activations for the same weights
+                cases.append((rand_i8((M, K), 70 + i), wq, torch.rand(M, generator=torch.Generator().manual_seed(80 + i)) * 0.05, sw))
+            wd, swd = wq.cuda(), sw.cuda()
+            srcs = [(c[0].cuda(), c[2].cuda()) for c in cases]
+            xd, sxd = torch.empty_like(srcs[0][0]), torch.empty_like(srcs[0][1])
+            outs = []
+            for (xs, ss) in srcs:
+                xd.copy_(xs)
+                sxd.copy_(ss)
+                outs.append(g.matmul_scaled(xd, wd, sxd, swd))
+            for (c, out) in zip(cases, outs):
+                assert_bits_equal(oracle, out, oracle.c_matmul_scaled(c[0], wq, c[2], sw), f"static weights {(M, N, K)}")
+    finally:
+        monkeypatch.delenv("GEMM_INT8_STATIC_WEIGHTS", raising=False)
+        g.reload_env()
+
+
 def test_smallm_split_k_scratch_is_left_zeroed(g, oracle):
     """The split-K kernel adds int32 partials into caller-provided scratch and must leave it zero-filled, so
     back-to-back calls sharing one buffer stay exact; also checks extreme values and ragged N."""
