@@ -406,7 +406,8 @@ int zero_output(void* out, int64_t bytes, cudaStream_t stream)
 // Small-M plan: token tile MT, number of K splits and pipeline depth.  Fitted on B200 with device-timed CUDA-graph
 // replays over HBM-cold weights (M in {1,16,64} x {4096x4096, 14336x4096, 4096x14336}): few weight tiles want the
 // largest cluster (8 splits: 32 tiles -> 256 CTAs), many weight tiles want one or two; for M >= 16 the reduction
-// costs more than a second split gains.  Two CTAs fit one SM (about 100 KB of shared memory each).
+// costs more than a second split gains (measured again with the one-barrier reduction: the same choices win).  Two CTAs
+// fit one SM (about 100 KB of shared memory each).
 // ---------------------------------------------------------------------------------------------------
 struct SmallMPlan {
     bool use;
@@ -459,12 +460,14 @@ int launch_smallm(DeviceState* st, int slot, const int8_t* x, const int8_t* w, S
 
 constexpr int kMaxClusterSplits = 8;  // portable thread-block cluster size
 
-template <int MT, int STAGES>
+// RECV: room behind the pipeline buffers for the partial sums the cluster peers send (needed when splits > 1).
+template <int MT, int STAGES, bool RECV>
 int launch_smallm_cluster(DeviceState* st, int slot, const int8_t* x, const int8_t* w, SmallMParams p,
                           const SmallMPlan& pl, cudaStream_t stream)
 {
     constexpr size_t stage = kSmallMTileN * kBK + ((MT * kBK + 1023) / 1024) * 1024;
-    constexpr size_t smem = STAGES * stage + 1024;
+    constexpr size_t smem = STAGES * stage + (RECV ? (MT + kMaxClusterSplits) * kSmallMTileN * 4 : 0) + 1024;
+    static_assert(smem <= 227 * 1024, "shared memory per CTA");
     auto kernel = smallm_cluster_kernel<MT, STAGES>;
     if (int rc = ensure_smem(st, slot, kernel, smem)) return rc;
     CUtensorMap mw, mx;
@@ -722,11 +725,23 @@ int gi8_matmul_scaled(const int8_t* x, const int8_t* y, const float* sx, const f
             q.out = out, q.sx = sx, q.sw = sw, q.status = st->status, q.ldo = N;
             q.M = (int)M, q.N = (int)N, q.K = (int)K, q.kb_per_split = pl.kb_per_split, q.splits = pl.splits;
             q.static_w = knobs().static_weights && knobs().pdl;
-            switch (pl.mt) {
-                case 16: return launch_smallm_cluster<16, 6>(st, 28, x, y, q, pl, s);
-                case 32: return launch_smallm_cluster<32, 5>(st, 29, x, y, q, pl, s);
-                case 64: return launch_smallm_cluster<64, 4>(st, 30, x, y, q, pl, s);
-                default: return launch_smallm_cluster<128, 3>(st, 31, x, y, q, pl, s);
+            // Pipeline depth: two CTAs share an SM (about 100 KB each, the receive area of a cluster CTA included).  A
+            // deeper pipeline with one CTA per SM measured slower even for grids of at most one CTA per SM: the next
+            // kernel's CTAs could no longer move in beside the running ones, and its set-up no longer overlapped.
+            if (pl.splits > 1) {
+                switch (pl.mt) {
+                    case 16: return launch_smallm_cluster<16, 5, true>(st, 48, x, y, q, pl, s);
+                    case 32: return launch_smallm_cluster<32, 4, true>(st, 49, x, y, q, pl, s);
+                    case 64: return launch_smallm_cluster<64, 3, true>(st, 50, x, y, q, pl, s);
+                    default: return launch_smallm_cluster<128, 3, true>(st, 51, x, y, q, pl, s);
+                }
+            } else {
+                switch (pl.mt) {
+                    case 16: return launch_smallm_cluster<16, 6, false>(st, 52, x, y, q, pl, s);
+                    case 32: return launch_smallm_cluster<32, 5, false>(st, 53, x, y, q, pl, s);
+                    case 64: return launch_smallm_cluster<64, 4, false>(st, 54, x, y, q, pl, s);
+                    default: return launch_smallm_cluster<128, 3, true>(st, 51, x, y, q, pl, s);
+                }
             }
         }
     }

@@ -243,10 +243,13 @@ smallm_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
 
 // ---------------------------------------------------------------------------------------------------
 // Cluster variant: the SPLITS CTAs that share one weight tile form a thread-block cluster (1 x SPLITS x 1,
-// SPLITS <= 8).  Each CTA parks its int32 partial tile in its own shared memory; after a cluster barrier,
-// CTA r sums token rows r, r + SPLITS, ... over all peers through distributed shared memory, applies the
-// scales and stores bf16.  No global scratch, no atomics, and the sum is exact whatever the order.
-// The two cluster barriers are hardware barriers that every thread of every CTA reaches unconditionally.
+// SPLITS <= 8).  Token row m belongs to CTA m % SPLITS: every CTA sends its int32 partials of that row straight
+// from registers into the owner's receive area (remote shared-memory stores, which do not stall the sender);
+// after ONE cluster barrier each owner sums what it received from its own shared memory, applies the scales and
+// stores bf16.  After that barrier nobody touches a peer's memory, so CTAs leave independently.  The receive
+// area lies behind the pipeline buffers (a fast peer may send while the owner is still streaming weights).
+// No global scratch, no atomics, and the sum is exact whatever the order.  The cluster barrier is a hardware
+// barrier that every thread of every CTA reaches unconditionally.
 // ---------------------------------------------------------------------------------------------------
 template <int MT, int STAGES>
 __global__ void __launch_bounds__(kSmallMThreads)
@@ -260,7 +263,6 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     constexpr uint32_t kStageBytes = kBytesW + kBytesXPad;
     constexpr uint32_t kTmemCols = MT < 32 ? 32 : MT;
     constexpr uint32_t kIdesc = make_idesc_i8(kSmallMTileN, MT, false);
-    static_assert(STAGES * kStageBytes >= MT * kSmallMTileN * 4, "partial tile must fit in the pipeline buffers");
 
     extern __shared__ uint8_t smem_raw[];
     // The dynamic shared window starts at the same offset in every CTA of the cluster, so the aligned base
@@ -272,6 +274,7 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     __shared__ __align__(8) uint64_t bar_acc_full;
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile uint32_t abort_flag;
+    __shared__ float sx_s[MT];
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -326,7 +329,12 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
     tcgen05_fence_after_sync();
     pdl_wait();  // every thread: scales are read and the output is written only after the previous kernel is done
     const uint32_t tmem_base = tmem_base_slot;
-    int32_t* partial = reinterpret_cast<int32_t*>(smem);  // [MT][128], reuses the pipeline buffers once drained
+    // [sender][row of this owner][128] int32, behind the pipeline buffers
+    int32_t* recv = reinterpret_cast<int32_t*>(smem + STAGES * kStageBytes);
+    const uint32_t nranks = static_cast<uint32_t>(p.splits);
+    const uint32_t my_rank = p.splits > 1 ? cluster_cta_rank() : 0u;
+    const uint32_t rows_per_owner = (static_cast<uint32_t>(p.M) + nranks - 1) / nranks;
+    float col_scale = 0.0f;  // of this thread's output column (epilogue warps)
 
     if (warp == 0) {
         if (lane == 0) {
@@ -377,14 +385,19 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             if (ok) umma_commit(&bar_acc_full);
         }
     } else {
-        // epilogue warps: tensor memory -> this CTA's partial tile in shared memory (or straight to global)
+        // epilogue warps: tensor memory -> global (one split) or -> the row owners' receive areas
         const int quarter = warp & 3;
         const int n_local = quarter * 32 + lane;
         const int n = tile_n * kSmallMTileN + n_local;
+        // The scales are fetched while the weights stream, not between the last MMA and the stores.
+        col_scale = n < p.N ? __ldg(p.sw + n) : 0.0f;
+        {
+            const int t = static_cast<int>(threadIdx.x) - 64;
+            if (t < MT) sx_s[t] = t < p.M ? __ldg(p.sx + t) : 0.0f;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
         bool ok = true;
         if (num_kb > 0) {
-            // bar_acc_full completes only after every MMA has finished reading the pipeline buffers, so they
-            // can be overwritten with the partial tile from here on.
             if (!wait_or_abort(&bar_acc_full, 0, &abort_flag)) {
                 if (lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
                 ok = false;
@@ -393,6 +406,8 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             tcgen05_fence_after_sync();
         }
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t recv_mine = smem_u32(recv) + (my_rank * rows_per_owner * kSmallMTileN + n_local) * 4u;
+        uint32_t owner = 0, row_local = 0;  // of token row c + j, kept incrementally
 #pragma unroll
         for (int c = 0; c < MT; c += 16) {
             uint32_t t16[16];
@@ -405,45 +420,41 @@ smallm_cluster_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
             }
             if (p.splits == 1) {
                 if (n < p.N) {
-                    const float col_scale = __ldg(p.sw + n);
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (c + j < p.M) {
-                            const float t = __ldg(p.sx + c + j) * col_scale;
+                        if (c + j < p.M)
                             static_cast<uint16_t*>(p.out)[static_cast<int64_t>(c + j) * p.ldo + n] =
-                                to_bf16_bits(__int2float_rn(static_cast<int32_t>(t16[j])) * t);
-                        }
+                                to_bf16_bits(__int2float_rn(static_cast<int32_t>(t16[j])) * (sx_s[c + j] * col_scale));
                 }
             } else {
 #pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (c + j < p.M) partial[(c + j) * kSmallMTileN + n_local] = static_cast<int32_t>(t16[j]);
+                for (int j = 0; j < 16; ++j) {
+                    if (c + j < p.M)
+                        st_dsmem_u32(map_to_cta(recv_mine + row_local * (kSmallMTileN * 4u), owner), t16[j]);
+                    if (++owner == nranks) owner = 0, ++row_local;
+                }
             }
         }
     }
 
     tcgen05_fence_before_sync();
-    __syncthreads();
     if (p.splits > 1) {
-        cluster_sync_all();  // every CTA's partial tile is complete and visible cluster-wide
+        cluster_sync_all();  // every partial has landed in its owner's receive area
         if (warp >= 2) {
             const int n_local = (warp & 3) * 32 + lane;
             const int n = tile_n * kSmallMTileN + n_local;
-            const uint32_t my_rank = cluster_cta_rank();
-            const uint32_t nranks = static_cast<uint32_t>(p.splits);
-            const float col_scale = n < p.N ? __ldg(p.sw + n) : 0.0f;
-            for (int m = static_cast<int>(my_rank); m < p.M; m += static_cast<int>(nranks)) {
-                const uint32_t local = smem_u32(partial + m * kSmallMTileN + n_local);
+            uint32_t row_local = 0;
+            for (int m = static_cast<int>(my_rank); m < p.M; m += static_cast<int>(nranks), ++row_local) {
                 int32_t total = 0;
-                for (uint32_t r = 0; r < nranks; ++r) total += ld_dsmem_s32(map_to_cta(local, r));
-                if (n < p.N) {
-                    const float t = __ldg(p.sx + m) * col_scale;
+                for (uint32_t r = 0; r < nranks; ++r)
+                    total += recv[(r * rows_per_owner + row_local) * kSmallMTileN + n_local];
+                if (n < p.N)
                     static_cast<uint16_t*>(p.out)[static_cast<int64_t>(m) * p.ldo + n] =
-                        to_bf16_bits(__int2float_rn(total) * t);
-                }
+                        to_bf16_bits(__int2float_rn(total) * (sx_s[m] * col_scale));
             }
         }
-        cluster_sync_all();  // nobody exits (and frees its shared memory) while a peer may still read it
+    } else {
+        __syncthreads();
     }
     if (warp == 1) {
         __syncwarp();

@@ -415,6 +415,11 @@ GI8_DEVICE uint32_t map_to_cta(uint32_t local_smem_addr, uint32_t rank)
     return r;
 }
 
+GI8_DEVICE void st_dsmem_u32(uint32_t cluster_addr, uint32_t v)
+{
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
 GI8_DEVICE int32_t ld_dsmem_s32(uint32_t cluster_addr)
 {
     int32_t v;
