@@ -64,7 +64,7 @@ struct Knobs {
     bool tma_store = true;
     bool pdl = true;
     int splits = 0;
-    int bw_halves = 2;
+    int bw_halves = 0;   // 0: column halves for the two-CTA tile, N = 256 MMAs for the one-CTA 256-wide tile
     int bw_issuers = 0;  // 0: one for the 256-wide tile, two for the narrower ones
     // The caller promises that the weight operand of the small-M path is not written by the kernel that precedes the
     // call in its stream (weights quantised ahead of time): its first tiles are then requested before that kernel ends.
@@ -83,7 +83,7 @@ void load_knobs()
     if (const char* e = getenv("GEMM_INT8_TMA_STORE")) k.tma_store = e[0] != '0';
     if (const char* e = getenv("GEMM_INT8_PDL")) k.pdl = e[0] != '0';
     if (const char* e = getenv("GEMM_INT8_SPLITS")) k.splits = atoi(e);
-    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 1 ? 1 : 2;
+    if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 1 ? 1 : atoi(e) == 2 ? 2 : 0;
     if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 2 ? 2 : atoi(e) == 1 ? 1 : 0;
     if (const char* e = getenv("GEMM_INT8_STATIC_WEIGHTS")) k.static_weights = e[0] == '1';
     g_knobs = k;
@@ -232,9 +232,11 @@ int check_common(const void* x, const void* y, const void* out, int64_t M, int64
 // form's cycles per K block, fitted on B200 from device-timed runs (8192^3, 2048 x 11008 x 4096, 128..512 x 8192 x
 // 8192 and the reference benchmark's layer shapes, timed back to back):
 //   dense      256 x 256 two-CTA tile (74 slots) 580 | 128 x 256: 655 | 128 x 128: 465 | 128 x 64: 330
-//   blockwise  128 x 256: 990 | 128 x 128: 650 | 128 x 64: 490   (the two-CTA form measures the same as 128 x 256
-//              and stays a selectable variant)
-// The table is data: kTileForms below.  The narrow tiles cost more per column (the tensor-core instruction is issue
+//   blockwise  128 x 256 (N = 256 MMAs, one issuer): 950 | 256 x 256 two-CTA tile (column halves): 920, but only
+//              ahead on long runs (16384 x 57344 x 8192: 8.72 against 9.00 ms; 16384 x 8192 x 28672: 4.63 against
+//              4.85 ms; level at 8192^3; behind below that), hence its minimum number of waves
+//              | 128 x 128: 650 | 128 x 64: 490
+// The table is data: kDenseForms / kBlockwiseForms below.  The narrow tiles cost more per column (the tensor-core instruction is issue
 // bound below N = 128, and the per-K-block hand-overs do not shrink with the tile) and only pay when the wide tile
 // would leave most SMs without work.
 // ---------------------------------------------------------------------------------------------------
@@ -242,15 +244,16 @@ struct TileForm {
     int bn;
     bool pair;
     double kblock_cycles;
+    int min_waves;  // the form is considered only for grids of at least this many waves
 };
-constexpr TileForm kDenseForms[] = {{256, true, 580.0}, {256, false, 655.0}, {128, false, 465.0}, {64, false, 330.0}};
-constexpr TileForm kBlockwiseForms[] = {{256, false, 990.0}, {128, false, 650.0}, {64, false, 490.0}};
+constexpr TileForm kDenseForms[] = {{256, true, 580.0, 0}, {256, false, 655.0, 0}, {128, false, 465.0, 0}, {64, false, 330.0, 0}};
+constexpr TileForm kBlockwiseForms[] = {{256, true, 920.0, 20}, {256, false, 950.0, 0}, {128, false, 650.0, 0}, {64, false, 490.0, 0}};
 
 int pick_bn(int64_t M, int64_t N, int sms, bool blockwise, bool* pair = nullptr)
 {
     if (pair) *pair = false;
     const TileForm* forms = blockwise ? kBlockwiseForms : kDenseForms;
-    const int n_forms = blockwise ? 3 : 4;
+    const int n_forms = 4;
     int best = 256;
     double best_cost = 1e300;
     for (int i = 0; i < n_forms; ++i) {
@@ -260,6 +263,7 @@ int pick_bn(int64_t M, int64_t N, int sms, bool blockwise, bool* pair = nullptr)
         const int64_t tiles = ((M + tile_m - 1) / tile_m) * ((N + f.bn - 1) / f.bn);
         const int64_t slots = f.pair ? sms / 2 : sms;
         const int64_t waves = (tiles + slots - 1) / slots;
+        if (waves < f.min_waves) continue;
         // (a wave also pays a fixed part per tile: prologue, epilogue, tile turnover -- about 20 K blocks' worth at
         // K = 4096; the model only ranks forms for one K, so it enters as a small constant)
         const double cost = static_cast<double>(waves) * (f.kblock_cycles + 16.0);
@@ -619,8 +623,9 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
     if (forced != VAR_AUTO) return kVariantNames[forced];
     if (kind == 1 && plan_smallm(M, N, K, sms, false).use) return "smallm_cluster";
     if (kind == 2) {
-        const int bn = pick_bn(M, N, sms, true);
-        return bn == 256 ? "blockwise_bn256" : bn == 128 ? "blockwise_bn128" : "blockwise_bn64";
+        bool pair = false;
+        const int bn = pick_bn(M, N, sms, true, &pair);
+        return pair ? "blockwise_pair" : bn == 256 ? "blockwise_bn256" : bn == 128 ? "blockwise_bn128" : "blockwise_bn64";
     }
     bool pair = false;
     const int bn = pick_bn(M, N, sms, false, &pair);
@@ -985,7 +990,7 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mx, my, mo, p));                            \
     } while (0)
     const bool two = knobs().bw_issuers == 2 || (knobs().bw_issuers == 0 && bn < 256);
-    const bool halves = knobs().bw_halves == 2;
+    const bool halves = knobs().bw_halves == 2 || (knobs().bw_halves == 0 && pair);
     if (pair) {
         if (halves) GI8_LAUNCH_BW(256, 6, 2, 2, true, 21);
         else if (two) GI8_LAUNCH_BW(256, 6, 1, 2, true, 22);

@@ -402,19 +402,34 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         bool ok = true;
 
         // Waits for half h of the partial of the running K block; false on every lane if any lane gave up.  The
-        // common case is one successful test; the branch to the bounded spin is taken on a vote, which makes it
+        // barrier was already tested once, without blocking, before the arithmetic of the previous chunk
+        // (`polled`, see poll_next): in the steady state the MMAs are ahead, the test has succeeded and its latency
+        // lay under that arithmetic.  Otherwise the bounded wait runs; the branch is taken on a vote, which makes it
         // warp-uniform.
+        bool polled = false;
         auto wait_partial = [&](int h) {
-            const uint32_t bar = bar_done_0 + h * (STAGES * 8) + st_off;
-            bool got = mbar_try_wait_addr(bar, st_par);
-            if (!__all_sync(0xffffffffu, got)) {
-                got = wait_or_abort_addr(bar, st_par, &abort_flag);
+            if (!__all_sync(0xffffffffu, polled)) {
+                const uint32_t bar = bar_done_0 + h * (STAGES * 8) + st_off;
+                bool got = wait_or_abort_addr(bar, st_par, &abort_flag);
                 if (!got && lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
                 got = __all_sync(0xffffffffu, got);
                 if (!got) return false;
             }
             tcgen05_fence_after_sync();
             return true;
+        };
+        // Tests the barrier of the partial that follows half h of the running K block: the other half of the same K
+        // block, or half 0 of the next K block (the stage ring runs on across tiles; after the last K block of the
+        // last tile the test simply fails and is never looked at).
+        auto poll_next = [&](int h) {
+            uint32_t off = st_off, par = st_par;
+            int hn = h + 1;
+            if (hn == SPLIT) {
+                hn = 0;
+                off += 8;
+                if (off == STAGES * 8) off = 0, par ^= 1;
+            }
+            polled = mbar_test_wait_addr(bar_done_0 + hn * (STAGES * 8) + off, par);
         };
         // This warp's columns of half h of the running K block are in registers: one of the arrivals that hand the
         // half back to its MMA issuer.
@@ -474,7 +489,10 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                         uint32_t v[CHW];
                         tmem_ld_32x32b_x32(taddr + c * CHW, v);
                         tmem_ld_wait();
-                        if (c + 1 == NC) release_partial(h);
+                        if (c + 1 == NC) {
+                            release_partial(h);
+                            poll_next(h);
+                        }
 #pragma unroll
                         for (int q = 0; q < CHW / 2; ++q) promote_pair(acc[h * (SEGW / 2) + c * (CHW / 2) + q], v[2 * q], v[2 * q + 1], t2);
                     }

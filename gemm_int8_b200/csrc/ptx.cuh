@@ -105,6 +105,22 @@ GI8_DEVICE bool mbar_try_wait_addr(uint32_t bar_addr, uint32_t parity)
 
 GI8_DEVICE bool mbar_try_wait(uint64_t* bar, uint32_t parity) { return mbar_try_wait_addr(smem_u32(bar), parity); }
 
+// Non-blocking test of the phase with the given parity (try_wait may suspend the thread for a while).
+GI8_DEVICE bool mbar_test_wait_addr(uint32_t bar_addr, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar_addr), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
 // try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or about
 // `hint_ns` nanoseconds pass, instead of burning issue slots that working warps on the same scheduler need.
 GI8_DEVICE bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns)

@@ -187,13 +187,14 @@ int gi8_hadamard_quantize_token_block(const void* in, int in_dtype, int8_t* q, f
  * Forces a kernel variant for the calling process (tuning and tests); NULL or "" restores the fitted
  * per-shape dispatch that replaces the reference's shape table (csrc/kernels/gemm.cu:136-161).
  * Names: "dense_bn256", "dense_bn128", "dense_bn64" (tile width of the dense and of the blockwise kernel), "smallm"
- * (split-K through global scratch), "smallm_cluster" (split-K through distributed shared memory), "pair" (dense
- * entry points only: 256 x 256 two-CTA tiles with tcgen05.mma.cta_group::2), "auto".  Returns
+ * (split-K through global scratch), "smallm_cluster" (split-K through distributed shared memory), "pair" (256 x 256
+ * two-CTA tiles with tcgen05.mma.cta_group::2, dense and blockwise), "auto".  Returns
  * GI8_ERR_INVALID_ARGUMENT for an unknown name.
  */
 int gi8_force_variant(const char* name);
 
-/* Name of the variant the dispatch would pick for (kind, M, N, K); kind: 0 plain, 1 scaled, 2 blockwise. */
+/* Name of the variant the dispatch would pick for (kind, M, N, K); kind: 0 plain, 1 scaled, 2 blockwise (whose names
+ * read "blockwise_bn256", "blockwise_bn128", "blockwise_bn64", "blockwise_pair"). */
 const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K);
 
 /*
