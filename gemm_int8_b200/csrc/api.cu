@@ -992,9 +992,9 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     const bool two = knobs().bw_issuers == 2 || (knobs().bw_issuers == 0 && bn < 256);
     const bool halves = knobs().bw_halves == 2 || (knobs().bw_halves == 0 && pair);
     if (pair) {
-        if (halves) GI8_LAUNCH_BW(256, 6, 2, 2, true, 21);
-        else if (two) GI8_LAUNCH_BW(256, 6, 1, 2, true, 22);
-        else GI8_LAUNCH_BW(256, 6, 1, 1, true, 23);
+        if (halves) GI8_LAUNCH_BW(256, 4, 2, 2, true, 21);
+        else if (two) GI8_LAUNCH_BW(256, 4, 1, 2, true, 22);
+        else GI8_LAUNCH_BW(256, 4, 1, 1, true, 23);
     } else if (bn == 256) {
         if (halves) GI8_LAUNCH_BW(256, 4, 2, 2, false, 13);
         else if (two) GI8_LAUNCH_BW(256, 4, 1, 2, false, 15);

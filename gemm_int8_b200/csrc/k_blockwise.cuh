@@ -24,6 +24,11 @@
 // counts is instructions issued.  16 warps x 64 columns with 16-column loads and a biased accumulator written
 // back with tcgen05.st: 860-920.  8 warps x 128 columns, 32-column loads: biased accumulator with write-back 665-685
 // (the stores alone cost 140), cvt + fma.f32x2 without any write-back 545-580, against 512 for the MMAs.
+// The same was measured in this kernel itself, with the column groups made a template parameter: twelve promotion
+// warps (three per scheduler) on a 128 x 192 tile ran 15-20 % slower than eight on 128 x 256, sixteen (four per
+// scheduler, 112 registers each, 16-column loads) 40-50 % slower -- every warp repeats the per-K-block bookkeeping
+// (barrier test, hand-back, scale product, counters), and those instructions share the half-rate integer pipe
+// with the conversions, which is the busiest unit (two cycles per cvt.rn.f32.s32: 512 of the K block's cycles).
 //
 // Barrier protocol (every wait is a parity wait, so it must hold that a barrier cannot complete a second phase
 // before the waiter has consumed the first; the comment at each barrier says what gates its next phase):
@@ -42,6 +47,8 @@
 //   buffers b % 2 == j (STAGES and NBUF are even): every barrier still has exactly one issuing waiter, which sees
 //   all its phases.
 #pragma once
+
+#include <type_traits>
 
 #include "k_dense.cuh"
 
@@ -407,10 +414,11 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         // lay under that arithmetic.  Otherwise the bounded wait runs; the branch is taken on a vote, which makes it
         // warp-uniform.
         bool polled = false;
-        auto wait_partial = [&](int h) {
+        // (so, sp): byte offset of the stage's barrier in its ring and the parity awaited there.
+        auto wait_partial = [&](int h, uint32_t so, uint32_t sp) {
             if (!__all_sync(0xffffffffu, polled)) {
-                const uint32_t bar = bar_done_0 + h * (STAGES * 8) + st_off;
-                bool got = wait_or_abort_addr(bar, st_par, &abort_flag);
+                const uint32_t bar = bar_done_0 + h * (STAGES * 8) + so;
+                bool got = wait_or_abort_addr(bar, sp, &abort_flag);
                 if (!got && lane == 0) raise_error(p.status, &abort_flag, ERR_TIMEOUT_EPILOGUE);
                 got = __all_sync(0xffffffffu, got);
                 if (!got) return false;
@@ -418,28 +426,27 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             tcgen05_fence_after_sync();
             return true;
         };
-        // Tests the barrier of the partial that follows half h of the running K block: the other half of the same K
-        // block, or half 0 of the next K block (the stage ring runs on across tiles; after the last K block of the
+        // Tests the barrier of the partial that follows half h of the K block at (so, sp): the other half of the same
+        // K block, or half 0 of the next K block (the stage ring runs on across tiles; after the last K block of the
         // last tile the test simply fails and is never looked at).
-        auto poll_next = [&](int h) {
-            uint32_t off = st_off, par = st_par;
+        auto poll_next = [&](int h, uint32_t so, uint32_t sp) {
             int hn = h + 1;
             if (hn == SPLIT) {
                 hn = 0;
-                off += 8;
-                if (off == STAGES * 8) off = 0, par ^= 1;
+                so += 8;
+                if (so == STAGES * 8) so = 0, sp ^= 1;
             }
-            polled = mbar_test_wait_addr(bar_done_0 + hn * (STAGES * 8) + off, par);
+            polled = mbar_test_wait_addr(bar_done_0 + hn * (STAGES * 8) + so, sp);
         };
-        // This warp's columns of half h of the running K block are in registers: one of the arrivals that hand the
-        // half back to its MMA issuer.
-        auto release_partial = [&](int h) {
+        // This warp's columns of half h of the K block in the partial buffer whose barrier lies at byte offset bo are
+        // in registers: one of the arrivals that hand the half back to its MMA issuer.
+        auto release_partial = [&](int h, uint32_t bo) {
             tcgen05_fence_before_sync();
             __syncwarp();
             if constexpr (PAIR) {
-                if (elect_one()) mbar_arrive_cluster(bar_empty_0 + h * (NBUF * 8) + buf_off);
+                if (elect_one()) mbar_arrive_cluster(bar_empty_0 + h * (NBUF * 8) + bo);
             } else {
-                mbar_arrive_elected_addr(bar_empty_0 + h * (NBUF * 8) + buf_off);
+                mbar_arrive_elected_addr(bar_empty_0 + h * (NBUF * 8) + bo);
             }
         };
         auto next_k_block = [&]() {
@@ -448,6 +455,12 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             buf_off += 8, buf_col += BN;
             if (buf_off == NBUF * 8) buf_off = 0, buf_col = 0;
         };
+        // With four stages, two partial buffers and K blocks handled four at a time (the vector-scale path, whose K
+        // block count is a multiple of four), every tile starts at stage 0 and buffer 0: the ring positions of the four
+        // K blocks of a group are compile-time constants and only the parity, flipped once per group, lives in a
+        // register.  That removes the counter arithmetic (about ten instructions per warp and K block on the integer
+        // pipe, which the conversions keep busiest).
+        constexpr bool kStaticRing = STAGES == 4 && NBUF == 2;
 
         for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
             int mb, nb;
@@ -478,28 +491,36 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             // chunks: no gain, the 32-column form spills.  64-column loads: no gain.  Sending a third of the pairs
             // through an integer multiply-add on the other pipe instead of cvt: no gain.  Leaving the grouping of
             // conversions and multiply-adds to the compiler (non-volatile statements): the same cycle count.)
-            auto k_block = [&](const float (&t)[SPLIT]) -> bool {
+            // J >= 0: K block J of a group of four under kStaticRing; J < 0: the running counters.
+            auto k_block = [&](const float (&t)[SPLIT], auto jc) -> bool {
+                constexpr int J = decltype(jc)::value;
+                const uint32_t so = J >= 0 ? static_cast<uint32_t>(J * 8) : st_off;
+                const uint32_t sp = st_par;
+                const uint32_t bo = J >= 0 ? static_cast<uint32_t>((J & 1) * 8) : buf_off;
+                const uint32_t bc = J >= 0 ? static_cast<uint32_t>((J & 1) * BN) : buf_col;
 #pragma unroll
                 for (int h = 0; h < SPLIT; ++h) {
-                    if (!wait_partial(h)) return false;
+                    if (!wait_partial(h, so, sp)) return false;
                     const uint64_t t2 = splat_f32x2(t[h]);
-                    const uint32_t taddr = tm_warp + buf_col + h * NSUB;
+                    const uint32_t taddr = tm_warp + bc + h * NSUB;
 #pragma unroll
                     for (int c = 0; c < NC; ++c) {
                         uint32_t v[CHW];
                         tmem_ld_32x32b_x32(taddr + c * CHW, v);
                         tmem_ld_wait();
                         if (c + 1 == NC) {
-                            release_partial(h);
-                            poll_next(h);
+                            release_partial(h, bo);
+                            poll_next(h, so, sp);
                         }
 #pragma unroll
                         for (int q = 0; q < CHW / 2; ++q) promote_pair(acc[h * (SEGW / 2) + c * (CHW / 2) + q], v[2 * q], v[2 * q + 1], t2);
                     }
                 }
-                next_k_block();
+                if constexpr (J < 0) next_k_block();
+                else if constexpr (J == 3) st_par ^= 1;
                 return true;
             };
+            using Dyn = std::integral_constant<int, -1>;
 
             if (p.scale_vec) {
                 // Scales of four K blocks per load (16 bytes per row): a quarter of the load instructions and of
@@ -521,16 +542,16 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                     float t[SPLIT];
 #pragma unroll
                     for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_c.x, sw_c[h].x);
-                    ok = k_block(t);
+                    ok = k_block(t, std::integral_constant<int, kStaticRing ? 0 : -1>{});
 #pragma unroll
                     for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_c.y, sw_c[h].y);
-                    ok = ok && k_block(t);
+                    ok = ok && k_block(t, std::integral_constant<int, kStaticRing ? 1 : -1>{});
 #pragma unroll
                     for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_c.z, sw_c[h].z);
-                    ok = ok && k_block(t);
+                    ok = ok && k_block(t, std::integral_constant<int, kStaticRing ? 2 : -1>{});
 #pragma unroll
                     for (int h = 0; h < SPLIT; ++h) t[h] = mul_in_place(sa_c.w, sw_c[h].w);
-                    ok = ok && k_block(t);
+                    ok = ok && k_block(t, std::integral_constant<int, kStaticRing ? 3 : -1>{});
                     sa_c = sa_n;
 #pragma unroll
                     for (int h = 0; h < SPLIT; ++h) sw_c[h] = sw_n[h];
@@ -559,7 +580,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #pragma unroll
                         for (int h = 0; h < SPLIT; ++h) sw_q[j][h] = ldg_in_place(p.sw + (sw_off[h] + kb + 2));
                     }
-                    return k_block(t);
+                    return k_block(t, Dyn{});
                 };
                 for (int kb = 0; kb < num_kb && ok; kb += 2) {
                     ok = k_block_scalar(kb, 0);
