@@ -490,7 +490,12 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             // (Issuing the next chunk's load before this chunk's arithmetic was tried with 32- and with 16-column
             // chunks: no gain, the 32-column form spills.  64-column loads: no gain.  Sending a third of the pairs
             // through an integer multiply-add on the other pipe instead of cvt: no gain.  Leaving the grouping of
-            // conversions and multiply-adds to the compiler (non-volatile statements): the same cycle count.)
+            // conversions and multiply-adds to the compiler (non-volatile statements): the same cycle count.  Writing
+            // the conversions one to sixteen pairs ahead of their multiply-adds: the same times to within the run-to-run
+            // spread -- the assembler schedules the block itself.  Sending every third to eighth pair through
+            // multiply-add-pipe instructions only (integer multiply-add with the bias 0x4B400000, packed subtract,
+            // packed fma), measured again after the barrier latencies had been hidden: 15-45 % slower on the one-CTA
+            // form, 2-4 % faster on the two-CTA form with column halves.)
             // J >= 0: K block J of a group of four under kStaticRing; J < 0: the running counters.
             auto k_block = [&](const float (&t)[SPLIT], auto jc) -> bool {
                 constexpr int J = decltype(jc)::value;
