@@ -13,7 +13,7 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 LIB_NAME = "libgemm_int8_b200.so"
 LIB_PATH = os.path.join(_PKG, LIB_NAME)
 SOURCES = [os.path.join(_PKG, "csrc", "api.cu")]
-HEADERS = [os.path.join(_PKG, "csrc", f) for f in ("ptx.cuh", "k_dense.cuh", "k_blockwise.cuh", "k_smallm.cuh", "k_quant.cuh")]
+HEADERS = [os.path.join(_PKG, "csrc", f) for f in ("ptx.cuh", "k_dense.cuh", "k_dense_splitk.cuh", "k_blockwise.cuh", "k_smallm.cuh", "k_quant.cuh")]
 HEADERS.append(os.path.join(os.path.dirname(_PKG), "include", "gemm_int8_b200.h"))
 
 NVCC_FLAGS = [

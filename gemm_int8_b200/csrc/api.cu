@@ -16,6 +16,7 @@
 #include "k_dense.cuh"
 #include "k_quant.cuh"
 #include "k_smallm.cuh"
+#include "k_dense_splitk.cuh"
 
 namespace {
 
@@ -69,6 +70,7 @@ struct Knobs {
     // The caller promises that the weight operand of the small-M path is not written by the kernel that precedes the
     // call in its stream (weights quantised ahead of time): its first tiles are then requested before that kernel ends.
     bool static_weights = false;
+    int tail_split = 1;  // dense kernels: 0 never split K, 1 when the model says it pays, 2 whenever it is possible
 };
 Knobs g_knobs;
 std::once_flag g_knobs_once;
@@ -85,6 +87,7 @@ void load_knobs()
     if (const char* e = getenv("GEMM_INT8_SPLITS")) k.splits = atoi(e);
     if (const char* e = getenv("GEMM_INT8_BW_HALVES")) k.bw_halves = atoi(e) == 1 ? 1 : atoi(e) == 2 ? 2 : 0;
     if (const char* e = getenv("GEMM_INT8_BW_ISSUERS")) k.bw_issuers = atoi(e) == 2 ? 2 : atoi(e) == 1 ? 1 : 0;
+    if (const char* e = getenv("GEMM_INT8_TAIL_SPLIT")) k.tail_split = atoi(e) == 0 ? 0 : atoi(e) == 2 ? 2 : 1;
     if (const char* e = getenv("GEMM_INT8_STATIC_WEIGHTS")) k.static_weights = e[0] == '1';
     g_knobs = k;
 }
@@ -249,7 +252,7 @@ struct TileForm {
 constexpr TileForm kDenseForms[] = {{256, true, 580.0, 0}, {256, false, 655.0, 0}, {128, false, 465.0, 0}, {64, false, 330.0, 0}};
 constexpr TileForm kBlockwiseForms[] = {{256, true, 920.0, 20}, {256, false, 950.0, 0}, {128, false, 650.0, 0}, {64, false, 490.0, 0}};
 
-int pick_bn(int64_t M, int64_t N, int sms, bool blockwise, bool* pair = nullptr)
+int pick_bn(int64_t M, int64_t N, int sms, bool blockwise, bool* pair = nullptr, double* cost_per_kb = nullptr)
 {
     if (pair) *pair = false;
     const TileForm* forms = blockwise ? kBlockwiseForms : kDenseForms;
@@ -272,6 +275,7 @@ int pick_bn(int64_t M, int64_t N, int sms, bool blockwise, bool* pair = nullptr)
             if (pair) *pair = f.pair;
         }
     }
+    if (cost_per_kb) *cost_per_kb = best_cost;
     return best;
 }
 
@@ -326,7 +330,7 @@ int launch_dense(DeviceState* st, int slot, const int8_t* x, const int8_t* y, De
     p.tiles_m = (p.M + kBM - 1) / kBM;
     p.tiles_n = (p.N + BN - 1) / BN;
     p.group_m = pick_group_m(p.K);
-    const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+    const int64_t tiles = p.tile_end > 0 ? p.tile_end : static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int grid = static_cast<int>(tiles < st->sm_count ? tiles : st->sm_count);
     kernel<<<grid, kDenseThreads, smem, stream>>>(mx, my, mo, p);
     GI8_CUDA(cudaGetLastError());
@@ -354,7 +358,7 @@ int launch_dense_pair(DeviceState* st, int slot, const int8_t* x, const int8_t* 
     p.tiles_m = (p.M + 2 * kBM - 1) / (2 * kBM);
     p.tiles_n = (p.N + BN - 1) / BN;
     p.group_m = pick_group_m(p.K) / 2 > 0 ? pick_group_m(p.K) / 2 : 1;
-    const int64_t tiles = static_cast<int64_t>(p.tiles_m) * p.tiles_n;
+    const int64_t tiles = p.tile_end > 0 ? p.tile_end : static_cast<int64_t>(p.tiles_m) * p.tiles_n;
     const int pairs = static_cast<int>(tiles < st->sm_count / 2 ? tiles : st->sm_count / 2);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * pairs, 1, 1);
@@ -372,18 +376,143 @@ int launch_dense_pair(DeviceState* st, int slot, const int8_t* x, const int8_t* 
     return GI8_OK;
 }
 
+// Split-K launch for tiles [tile_begin, tile_begin + units / halves) of the grid described by p (tiles_m, tiles_n,
+// group_m as the main launch set them).
+template <int EPI>
+int launch_dense_splitk(DeviceState* st, int slot, const int8_t* x, const int8_t* y, const DenseParams& p,
+                        const SplitKParams& q, cudaStream_t stream)
+{
+    constexpr size_t smem = static_cast<size_t>(kSplitKStages) * (kBM + kSplitKBN) * kBK + 1024;
+    auto kernel = dense_splitk_kernel<EPI>;
+    if (int rc = ensure_smem(st, slot, kernel, smem)) return rc;
+    CUtensorMap mx, my;
+    if (int rc = make_operand_map(&mx, x, p.M, p.K, kBM)) return rc;
+    if (int rc = make_operand_map(&my, y, p.N, p.K, kSplitKBN)) return rc;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(q.units * q.splits, 1, 1);
+    cfg.blockDim = dim3(kDenseThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = q.splits;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mx, my, p, q));
+    return GI8_OK;
+}
+
+// The last wave of a persistent grid costs as much as a full one however few tiles it holds.  When it is thin -- or
+// the whole grid is -- its tiles can go to the split-K kernel instead: `units` 128 x 256 tiles times S K-splits, S the
+// largest of 8, 4, 2 that keeps units x S CTAs within the machine and at least two K blocks per split.  Cost model
+// in the units of the tile-form table (cycles per K block): split if
+//   (waves - 1) x form + kb / S x 655 + fixed < what would run instead.
+// The fixed part was fitted on B200 (L2-cold runs): 16000 cycles when the split-K launch is the only one (its ramp-up
+// on cold operands, two cluster barriers, 128 KB of partials per CTA through distributed shared memory, stores of 8
+// bytes per thread), 26000 when it follows a main launch (a second, dependent launch on top).  With these numbers a
+// thin last wave moves only when one wave is long (K of about 8192 and more), and a thin grid when K is long against
+// its tile count (256 x 4096 x 28672: 62 -> 41 us; 512 x 4096 x 14336 and 128 x 8192 x 8192: level, left alone).
+constexpr double kSplitKBlockCycles = 655.0;   // one-CTA 128 x 256 tile
+constexpr double kTailFixedAlone = 16000.0;
+constexpr double kTailFixedAfterMain = 26000.0;
+struct TailPlan {
+    bool use;
+    int tile_end;  // tiles left to the main launch
+    SplitKParams q;
+};
+
+// `now_per_kb` >= 0: the cost (per K block) of what would run instead, when that is not the form whose grid is split.
+TailPlan plan_tail(int64_t M, int64_t N, int64_t K, bool pair, double form_cycles, int sms, double now_per_kb = -1.0)
+{
+    TailPlan t{};
+    if (knobs().tail_split == 0) return t;
+    const int tile_m = pair ? 2 * kBM : kBM;
+    const int64_t tiles = ((M + tile_m - 1) / tile_m) * ((N + 255) / 256);
+    const int64_t slots = pair ? sms / 2 : sms;
+    const int64_t waves = (tiles + slots - 1) / slots;
+    const int64_t rest = tiles - (waves - 1) * slots;       // tiles of the last wave
+    const int64_t units = rest * (pair ? 2 : 1);
+    const int kb = static_cast<int>((K + kBK - 1) / kBK);
+    int S = 0;
+    for (int c = 8; c >= 2; c /= 2)
+        if (units * c <= sms && kb / c >= 2) {
+            S = c;
+            break;
+        }
+    if (S == 0) return t;
+    const int kbs = (kb + S - 1) / S;
+    const double now = now_per_kb >= 0.0 ? now_per_kb * kb : static_cast<double>(waves) * kb * (form_cycles + 16.0);
+    const double split = static_cast<double>(waves - 1) * kb * (form_cycles + 16.0) + kbs * kSplitKBlockCycles + (waves > 1 ? kTailFixedAfterMain : kTailFixedAlone);
+    if (knobs().tail_split == 1 && split >= now) return t;
+    t.use = true;
+    t.tile_end = static_cast<int>((waves - 1) * slots);
+    t.q.tile_begin = t.tile_end;
+    t.q.units = static_cast<int>(units);
+    t.q.splits = S;
+    t.q.kb_per_split = kbs;
+    t.q.pair_grid = pair ? 1 : 0;
+    return t;
+}
+
+// The automatic choice for the dense entry points: tile form, and whether (part of) its grid goes to the split-K kernel.
+// A narrow-tile choice (few tiles) is also weighed against splitting the whole one-CTA 256-wide grid.
+struct DenseChoice {
+    int bn;
+    bool pair;
+    TailPlan tail;
+};
+
+DenseChoice choose_dense(int64_t M, int64_t N, int64_t K, int sms)
+{
+    DenseChoice c{};
+    double cost = 0.0;
+    c.bn = pick_bn(M, N, sms, false, &c.pair, &cost);
+    if (c.bn == 256) {
+        c.tail = plan_tail(M, N, K, c.pair, c.pair ? kDenseForms[0].kblock_cycles : kDenseForms[1].kblock_cycles, sms);
+    } else {
+        const TailPlan t = plan_tail(M, N, K, false, kDenseForms[1].kblock_cycles, sms, cost);
+        if (t.use && t.tile_end == 0) c.bn = 256, c.pair = false, c.tail = t;
+    }
+    return c;
+}
+
 template <int EPI>
 int dispatch_dense(DeviceState* st, const int8_t* x, const int8_t* y, DenseParams p, cudaStream_t stream)
 {
     const int forced = g_forced_variant;
-    if (forced == VAR_PAIR) return launch_dense_pair<EPI>(st, 45 + EPI, x, y, p, stream);
     int bn;
     bool pair = false;
+    TailPlan t{};
     switch (forced) {
+        case VAR_PAIR: bn = 256, pair = true; break;
         case VAR_DENSE_BN256: bn = 256; break;
         case VAR_DENSE_BN128: bn = 128; break;
         case VAR_DENSE_BN64: bn = 64; break;
-        default: bn = pick_bn(p.M, p.N, st->sm_count, false, &pair);
+        default: {
+            const DenseChoice c = choose_dense(p.M, p.N, p.K, st->sm_count);
+            bn = c.bn, pair = c.pair, t = c.tail;
+        }
+    }
+    // A forced 256-wide form still hands its last wave to the split-K kernel when that is forced too (tests).
+    if (forced != VAR_AUTO && bn == 256 && knobs().tail_split == 2)
+        t = plan_tail(p.M, p.N, p.K, pair, pair ? kDenseForms[0].kblock_cycles : kDenseForms[1].kblock_cycles, st->sm_count);
+    if constexpr (EPI != EPI_RAW_I32) {
+        if (t.use && p.vec_ok) {
+            DenseParams pm = p;
+            pm.tile_end = t.tile_end;
+            DenseParams pt = p;  // the grid description the split-K kernel numbers its tiles by
+            pt.tiles_m = static_cast<int>((p.M + (pair ? 2 * kBM : kBM) - 1) / (pair ? 2 * kBM : kBM));
+            pt.tiles_n = static_cast<int>((p.N + 255) / 256);
+            pt.group_m = pair ? (pick_group_m(p.K) / 2 > 0 ? pick_group_m(p.K) / 2 : 1) : pick_group_m(p.K);
+            if (t.tile_end > 0) {
+                if (int rc = pair ? launch_dense_pair<EPI>(st, 45 + EPI, x, y, pm, stream)
+                                  : launch_dense<256, 4, EPI>(st, EPI * 3 + 0, x, y, pm, stream))
+                    return rc;
+            }
+            return launch_dense_splitk<EPI>(st, 60 + (EPI == EPI_ALPHA_BF16 ? 0 : 1), x, y, pt, t.q, stream);
+        }
     }
     if (pair) return launch_dense_pair<EPI>(st, 45 + EPI, x, y, p, stream);
     if (bn == 256) return launch_dense<256, 4, EPI>(st, EPI * 3 + 0, x, y, p, stream);
@@ -627,8 +756,16 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
         const int bn = pick_bn(M, N, sms, true, &pair);
         return pair ? "blockwise_pair" : bn == 256 ? "blockwise_bn256" : bn == 128 ? "blockwise_bn128" : "blockwise_bn64";
     }
-    bool pair = false;
-    const int bn = pick_bn(M, N, sms, false, &pair);
+    const DenseChoice c = choose_dense(M, N, K, sms);
+    const bool pair = c.pair;
+    const int bn = c.bn;
+    if (c.tail.use) {
+        static const char* const names[2][2][4] = {
+            {{"", "dense_bn256+splitk2", "dense_bn256+splitk4", "dense_bn256+splitk8"}, {"", "splitk2", "splitk4", "splitk8"}},
+            {{"", "pair+splitk2", "pair+splitk4", "pair+splitk8"}, {"", "splitk2", "splitk4", "splitk8"}}};
+        const int si = c.tail.q.splits == 2 ? 1 : c.tail.q.splits == 4 ? 2 : 3;
+        return names[pair ? 1 : 0][c.tail.tile_end > 0 ? 0 : 1][si];
+    }
     return pair ? "pair" : bn == 256 ? "dense_bn256" : bn == 128 ? "dense_bn128" : "dense_bn64";
 }
 

@@ -49,6 +49,7 @@ struct DenseParams {
     int vec_ok;           // out is 16-byte aligned and ldo keeps every row 16-byte aligned
     int group_m;          // row-blocks per rasterisation band
     int tma_store;        // bf16 epilogues: stage 32 x 32 blocks in shared memory and write them with TMA stores
+    int tile_end;         // > 0: only tiles [0, tile_end) of the grid are computed here (the rest by the split-K launch)
     float alpha;
 };
 
@@ -130,7 +131,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int num_tiles = p.tiles_m * p.tiles_n;   // tiles_m counts kTileM-row tiles
+    const int num_tiles = p.tile_end > 0 ? p.tile_end : p.tiles_m * p.tiles_n;   // tiles_m counts kTileM-row tiles
     const int num_kb = (p.K + kBK - 1) / kBK;
     // PAIR: rank 0 is the leader (its bar_full and bar_acc_empty serve both CTAs); the pair is the scheduling unit.
     const uint32_t rank = PAIR ? cluster_cta_rank() : 0u;

@@ -194,7 +194,9 @@ int gi8_hadamard_quantize_token_block(const void* in, int in_dtype, int8_t* q, f
 int gi8_force_variant(const char* name);
 
 /* Name of the variant the dispatch would pick for (kind, M, N, K); kind: 0 plain, 1 scaled, 2 blockwise (whose names
- * read "blockwise_bn256", "blockwise_bn128", "blockwise_bn64", "blockwise_pair"). */
+ * read "blockwise_bn256", "blockwise_bn128", "blockwise_bn64", "blockwise_pair").  For the dense kernels "+splitkS"
+ * after a form's name means that the tiles of its last wave go to the split-K kernel with S splits, and "splitkS" alone
+ * that the whole grid does. */
 const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K);
 
 /*
@@ -220,7 +222,9 @@ int gi8_selftest_wait_timeout(void* stream);
 
 /*
  * The GEMM_INT8_* tuning variables (tile band height, TMA-store epilogue, programmatic dependent launch, K splits,
- * blockwise MMA shape and issuer count) are read once, when the library is first used; this reads them again.
+ * blockwise MMA shape and issuer count, GEMM_INT8_TAIL_SPLIT = 0 / 1 / 2: never / when the cost model says so / whenever
+ * possible send a thin last wave of the dense kernels to the split-K kernel) are read once, when the library is first
+ * used; this reads them again.
  * GEMM_INT8_STATIC_WEIGHTS=1 (default 0) is a promise rather than a tuning: the weight operand of gi8_matmul_scaled's
  * small-M path is not written by the work that directly precedes the call in its stream (weights quantised ahead of
  * time), so the kernel may request its first weight tiles while that work is still finishing.  Activations, scales

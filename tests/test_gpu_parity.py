@@ -157,6 +157,49 @@ def test_reference_benchmark_shapes(g, oracle):
         assert_bits_equal(oracle, out, oracle.c_matmul(a, b, 1.0), f"benchmark shape {n}x{k}")
 
 
+# ---------------------------------------------------------------------------------------- split-K tail of the dense kernels
+@pytest.mark.parametrize("variant", ["dense_bn256", "pair", None])
+def test_dense_split_k_tail(g, oracle, variant, monkeypatch):
+    """GEMM_INT8_TAIL_SPLIT=2 sends the last wave of the 256-wide forms (or the whole grid, when it is thin) to the
+    split-K cluster kernel whenever that is possible: results must stay the oracle's bits for the plain and the
+    per-token x per-channel entry points -- ragged M and N, a 256-row tile whose lower half lies below M, extreme
+    values, and grids of more than one wave (main launch + split-K launch)."""
+    monkeypatch.setenv("GEMM_INT8_TAIL_SPLIT", "2")
+    g.reload_env()
+    try:
+        g.force_variant(variant)
+        gen = torch.Generator().manual_seed(91)
+        shapes = [(130, 264, 400), (300, 1000, 2048), (257, 520, 4096), (256, 20480, 512), (512, 10240, 640),
+                  (100, 38400, 256), (1, 8, 256)]
+        for (M, N, K) in shapes:
+            x, y = rand_i8((M, K), M + 11), rand_i8((N, K), N + 11)
+            if K >= 2048:
+                x[0], y[0] = -128, -128   # the largest possible sums
+            xd, yd = x.cuda(), y.cuda()
+            for alpha in (1.0, -3.7):
+                out = g.matmul(xd, yd, alpha)
+                assert_bits_equal(oracle, out, oracle.c_matmul(x, y, alpha), f"split-K plain {variant} {(M, N, K)} alpha {alpha}")
+            if M > 64:   # (smaller M goes to the small-M kernel)
+                sx = torch.rand(M, generator=gen) * 0.05 + 1e-3
+                sw = torch.rand(N, generator=gen) * 0.05 + 1e-3
+                out = g.matmul_scaled(xd, yd, sx.cuda(), sw.cuda())
+                assert_bits_equal(oracle, out, oracle.c_matmul_scaled(x, y, sx, sw), f"split-K scaled {variant} {(M, N, K)}")
+        assert g.device_status() == 0
+    finally:
+        g.force_variant(None)
+        monkeypatch.delenv("GEMM_INT8_TAIL_SPLIT", raising=False)
+        g.reload_env()
+
+
+def test_dense_split_k_is_chosen_for_thin_last_waves(g):
+    """The dispatch hands a thin last wave, or a thin grid with a long K, to the split-K kernel (names as
+    gi8_pick_variant reports them) and leaves well-filled grids alone."""
+    assert g.pick_variant(0, 1024, 14336, 16384).endswith("+splitk8")
+    assert g.pick_variant(0, 256, 4096, 28672).startswith("splitk")
+    assert g.pick_variant(0, 8192, 8192, 8192) == "pair"
+    assert g.pick_variant(0, 1024, 4096, 4096) == "pair"
+
+
 # ---------------------------------------------------------------------------------------- scaled (per token x per channel)
 @pytest.mark.parametrize("variant", DENSE_VARIANTS + ["smallm", "smallm_cluster", None])
 def test_scaled_edge_shapes(g, oracle, variant):
