@@ -49,9 +49,9 @@ NOMINAL_INT8_TOPS = 4500.0
 # DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised under
 # profiles/: keyed by (workload, M, N, K).  Other shapes report null.
 NCU_TRAFFIC = {
-    ("blockwise_prefill", 2048, 11008, 4096): (67.1e6, "profiles/blockwise_gemm_kernel__blockwise_prefill_2048x11008x4096.md"),
+    ("blockwise_prefill", 2048, 11008, 4096): (66.5e6, "profiles/blockwise_gemm_kernel__blockwise_prefill_2048x11008x4096.md"),
     ("square8192", 8192, 8192, 8192): (444.3e6, "profiles/dense_gemm_kernel__square8192.md"),
-    ("decode", 16, 14336, 4096): (58.97e6, "profiles/smallm_cluster_kernel__decode_16x14336x4096.md"),
+    ("decode", 16, 14336, 4096): (58.94e6, "profiles/smallm_cluster_kernel__decode_16x14336x4096.md"),
 }
 
 WORKLOADS = {
@@ -266,18 +266,23 @@ def run_reference(args, rank):
 # ---------------------------------------------------------------------------------------------------------------
 # sweep: every other configuration, device-timed on one GPU with inputs generated on the device
 # ---------------------------------------------------------------------------------------------------------------
-def _time_back_to_back(torch, fn, flush, iters, warm=3):
-    """Median device time (ms) of fn over `iters` launches, each preceded by an L2 flush outside the timed pair."""
-    for _ in range(warm):
-        fn()
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
-    for a, b in ev:
-        flush.max()
-        a.record()
-        fn()
-        b.record()
+def _time_interleaved(torch, fns, flush, iters, warm=3):
+    """Median device time (ms) of each function in `fns` over `iters` launches, every launch preceded by an L2 flush
+    outside its timed pair.  The functions take turns (a, b, c, a, b, c, ...), so that all of them see the same clock
+    and thermal state: timed one after the other, the ratio between two libraries moved by 20 % from run to run."""
+    for fn in fns:
+        for _ in range(warm):
+            fn()
+    ev = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)] for _ in fns]
+    for i in range(iters):
+        for j, fn in enumerate(fns):
+            a, b = ev[j][i]
+            flush.max()
+            a.record()
+            fn()
+            b.record()
     torch.cuda.synchronize()
-    return statistics.median(a.elapsed_time(b) for a, b in ev)
+    return [statistics.median(a.elapsed_time(b) for a, b in e) for e in ev]
 
 
 def _time_graph_rotating(torch, make_call, sets, replays=5):
@@ -327,8 +332,10 @@ def reference_kernel_times(shapes):
         return {}
 
 
-def run_sweep(torch, g, dev, flush, peaks):
+def run_sweep(torch, g, dev, flush, peaks, sections=None):
+    """sections: None for all, or a subset of {'plain', 'blockwise', 'decode', 'quant'}."""
     rows = []
+    want = lambda name: sections is None or name in sections  # noqa: E731
     gen = torch.Generator(device=dev).manual_seed(99)
 
     def ri8(shape):
@@ -353,14 +360,18 @@ def run_sweep(torch, g, dev, flush, peaks):
     # plain: config 1, the target squares and the reference benchmark's nine layer shapes (benchmark.py:56-62)
     plain = [("1", 1024, 4096, 4096), ("target", 8192, 8192, 8192), ("target", 16384, 16384, 16384)]
     plain += [("reference benchmark", m, n, k) for m in (512, 1024, 2048) for (n, k) in ((4096, 4096), (14336, 4096), (4096, 14336))]
-    ref_us = reference_kernel_times([(m, n, k) for (_, m, n, k) in plain])
+    if not want("plain"):
+        plain = []
+    ref_us = reference_kernel_times([(m, n, k) for (_, m, n, k) in plain]) if plain else {}
     for (cfg, M, N, K) in plain:
         x, y = ri8((M, K)), ri8((N, K))
         xb, yb = x.bfloat16(), y.bfloat16()
-        iters = 5 if M * N * K > 1e12 else 20
-        t = _time_back_to_back(torch, lambda: g.matmul(x, y, 1.0), flush, iters)
-        tb = _time_back_to_back(torch, lambda: torch.matmul(xb, yb.t()), flush, iters)
-        ti = _time_back_to_back(torch, lambda: torch._int_mm(x, y.t()), flush, iters) if M > 16 else None
+        iters = 5 if M * N * K > 1e12 else 30
+        fns = [lambda: g.matmul(x, y, 1.0), lambda: torch.matmul(xb, yb.t())]
+        if M > 16:
+            fns.append(lambda: torch._int_mm(x, y.t()))
+        ts = _time_interleaved(torch, fns, flush, iters)
+        t, tb, ti = ts[0], ts[1], (ts[2] if M > 16 else None)
         extra = {"cublaslt_int8_us": round(ti * 1e3, 2) if ti else None}
         if f"{M}x{N}x{K}" in ref_us:
             extra["reference_sm80_kernel_us"] = round(ref_us[f"{M}x{N}x{K}"], 2)
@@ -369,17 +380,16 @@ def run_sweep(torch, g, dev, flush, peaks):
     # blockwise: config 2 and the Llama-70B sweep (config 4)
     bw = [("2", 2048, 11008, 4096)]
     bw += [("4", m, n, k) for (k, n) in ((8192, 10240), (8192, 8192), (8192, 57344), (28672, 8192)) for m in (128, 512, 2048, 8192, 16384)]
-    for (cfg, M, N, K) in bw:
+    for (cfg, M, N, K) in (bw if want("blockwise") else []):
         x, y = ri8((M, K)), ri8((N, K))
         sa, sw = rf((M, K // 128)), rf((-(-N // 128), K // 128))
         xb, yb = x.bfloat16(), y.bfloat16()
-        iters = 5 if M * N * K > 1e12 else 20
-        t = _time_back_to_back(torch, lambda: g.matmul_blockwise(x, y, sa, sw), flush, iters)
-        tb = _time_back_to_back(torch, lambda: torch.matmul(xb, yb.t()), flush, iters)
+        iters = 5 if M * N * K > 1e12 else 30
+        t, tb = _time_interleaved(torch, [lambda: g.matmul_blockwise(x, y, sa, sw), lambda: torch.matmul(xb, yb.t())], flush, iters)
         entry(cfg, "blockwise", M, N, K, t, tb)
         del x, y, xb, yb, sa, sw
     # decode (config 3): HBM-bound, launch-bound; CUDA-graph replays over rotating weight copies
-    for (K, N) in ((4096, 4096), (4096, 14336), (14336, 4096)):
+    for (K, N) in (((4096, 4096), (4096, 14336), (14336, 4096)) if want("decode") else ()):
         n_sets = max(4, int(2.2 * 126e6 // (N * K)) + 1)
         ws = [ri8((N, K)) for _ in range(n_sets)]
         wbs = [w.bfloat16() for w in ws[: max(2, n_sets // 2)]]
@@ -391,6 +401,21 @@ def run_sweep(torch, g, dev, flush, peaks):
             tb = _time_graph_rotating(torch, lambda w: torch.matmul(xb, w.t()), wbs)
             entry("3", "scaled", M, N, K, t, tb)
         del ws, wbs
+    # activation quantisers (the step before every W8A8 GEMM): HBM-bound; bytes = input + int8 output + fp32 scales
+    if want("quant"):
+        shapes = [(torch.bfloat16, 2048, 4096), (torch.bfloat16, 2048, 8192), (torch.bfloat16, 16384, 8192), (torch.bfloat16, 8192, 28672),
+                  (torch.float32, 2048, 8192), (torch.float32, 16384, 8192), (torch.float32, 8192, 28672)]
+        for (dt, M, K) in shapes:
+            a = torch.randn((M, K), device=dev, generator=gen, dtype=torch.float32).to(dt)
+            fns = [lambda: g.quantize_per_token_block(a), lambda: g.hadamard_quantize_per_token_block(a), lambda: g.quantize_per_token(a)]
+            names = ["quantize_per_token_block", "hadamard_quantize_per_token_block", "quantize_per_token"]
+            ts = _time_interleaved(torch, fns, flush, 20)
+            for nm, t in zip(names, ts):
+                n_sc = M if nm == "quantize_per_token" else M * -(-K // 128)
+                byts = M * K * a.element_size() + M * K + 4 * n_sc
+                rows.append({"config": "f1/f2", "kind": "quantize", "op": nm, "dtype": str(dt).replace("torch.", ""), "M": M, "K": K,
+                             "us": round(t * 1e3, 2), "gbs": round(byts / t / 1e6, 1), "frac_hbm": round(byts / t / 1e6 / peaks["hbm_gbs"], 4)})
+            del a
     return rows
 
 
@@ -407,6 +432,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--only-sweep", default="", help="skip the main workload and print only the named sweep sections "
+                    "(comma-separated: plain, blockwise, decode, quant) as one JSON line; used by the profiling commands")
     ap.add_argument("--gather", default="auto", choices=["auto", "fused", "nccl"],
                     help="N > 1: all-gather fused into the GEMM epilogue (peer stores; auto), or NCCL after it")
     args = ap.parse_args()
@@ -438,6 +465,16 @@ def main():
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=dev)
+
+    if args.only_sweep:
+        # Not a bench line: the named sweep sections alone, for the profiling commands under profiles/.
+        if world > 1:
+            raise SystemExit("--only-sweep runs on one GPU")
+        flush = torch.zeros(256 << 20, dtype=torch.uint8, device=dev).view(torch.int64)
+        peaks_, _ = load_peaks()
+        rows = run_sweep(torch, g, dev, flush, peaks_, sections=set(args.only_sweep.split(",")))
+        print(json.dumps({"sweep_only": sorted(set(args.only_sweep.split(","))), "kernel_status": g.device_status(), "sweep": rows}))
+        return
 
     name = args.workload
     M, N, K, kind = WORKLOADS[name]
@@ -688,7 +725,8 @@ def main():
             "roofline": roofline,
             "cpu_baseline": cb,
             "e2e": e2e,
-            "gpu_launches": args.steps,
+            # one GEMM kernel of this library per step; two where the dense dispatch adds a split-K launch for the last wave
+            "gpu_launches": args.steps * (2 if "+splitk" in g.pick_variant({"blockwise": 2, "scaled": 1}.get(kind, 0), M, n_local, K) else 1),
             "clocks": clock_summary,
             "kernel_status": status,
             "sweep": sweep,
