@@ -35,6 +35,26 @@ def test_version_and_error_string():
     assert isinstance(g._C.gi8_last_error(), bytes)
 
 
+def test_dispatch_table_choices_without_gpu():
+    """The per-shape dispatch is host arithmetic over a table (148 SMs assumed without a device): tile form by waves x
+    cycles, the two-CTA blockwise form only for long runs, the split-K kernel for thin grids with a long K and for thin
+    last waves of long-K shapes, and nothing split where the grid fills the machine."""
+    import gemm_int8_b200 as g
+
+    pv = g.pick_variant
+    assert pv(0, 8192, 8192, 8192) == "pair"                      # 13.8 waves of two-CTA tiles: no tail worth splitting
+    assert pv(0, 1024, 4096, 4096) == "pair"                      # config 1: under one wave
+    assert pv(0, 512, 4096, 4096) == "dense_bn128"                # few tiles, short K: narrow tiles, no split
+    assert pv(0, 256, 4096, 28672).startswith("splitk")           # few tiles, long K: whole grid split
+    assert pv(0, 1024, 14336, 16384) == "pair+splitk8"            # 3.03 waves of long tiles: the last two go to split-K
+    assert pv(0, 1024, 14336, 4096) == "pair"                     # the same grid with short tiles: a second launch costs more
+    assert pv(2, 2048, 11008, 4096) == "blockwise_bn256"
+    assert pv(2, 16384, 57344, 8192) == "blockwise_pair"          # config 5: 193 waves
+    assert pv(2, 128, 8192, 8192) == "blockwise_bn64"
+    assert pv(1, 16, 4096, 4096) == "smallm_cluster" and pv(1, 64, 14336, 4096) == "smallm_cluster"
+    assert pv(1, 2048, 4096, 4096) == "pair"                      # the scaled entry point above M = 64 is the dense kernel
+
+
 def test_host_side_validation_without_gpu():
     """Shape/pointer checks run before any CUDA call, so they are testable on a CPU-only box."""
     import gemm_int8_b200 as g
