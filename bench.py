@@ -400,6 +400,18 @@ def run_sweep(torch, g, dev, flush, peaks, sections=None):
             t = _time_graph_rotating(torch, lambda w: g.matmul_scaled(x, w, sx, swc), ws)
             tb = _time_graph_rotating(torch, lambda w: torch.matmul(xb, w.t()), wbs)
             entry("3", "scaled", M, N, K, t, tb)
+            if M == 16:
+                # The same with the library's static-weights option (the host promises that the weights are not written
+                # by the preceding kernel, true of this loop as of any decode loop over a loaded model): the first weight
+                # tiles are requested before the dependency wait.  Off by default; reported as a row of its own.
+                os.environ["GEMM_INT8_STATIC_WEIGHTS"] = "1"
+                g.reload_env()
+                try:
+                    t2 = _time_graph_rotating(torch, lambda w: g.matmul_scaled(x, w, sx, swc), ws)
+                finally:
+                    os.environ.pop("GEMM_INT8_STATIC_WEIGHTS", None)
+                    g.reload_env()
+                entry("3", "scaled", M, N, K, t2, tb, {"option": "GEMM_INT8_STATIC_WEIGHTS=1"})
         del ws, wbs
     # activation quantisers (the step before every W8A8 GEMM): HBM-bound; bytes = input + int8 output + fp32 scales
     if want("quant"):
