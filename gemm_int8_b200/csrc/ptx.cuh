@@ -53,10 +53,6 @@ GI8_DEVICE void mbar_init(uint64_t* bar, uint32_t count)
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
 }
 
-GI8_DEVICE void mbar_inval(uint64_t* bar)
-{
-    asm volatile("mbarrier.inval.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
 
 // Makes mbarrier initialisation visible to the async proxy (TMA, tcgen05.commit).
 GI8_DEVICE void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
@@ -120,51 +116,6 @@ GI8_DEVICE bool mbar_test_wait_addr(uint32_t bar_addr, uint32_t parity)
         : "memory");
     return ok != 0;
 }
-
-// try_wait with a suspend-time hint: the thread sleeps in hardware until the phase completes or about
-// `hint_ns` nanoseconds pass, instead of burning issue slots that working warps on the same scheduler need.
-GI8_DEVICE bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
-        : "memory");
-    return ok != 0;
-}
-
-// Polls the barrier up to `tries` times in a loop of three instructions per poll (try_wait, branch, counter),
-// with no integer-pipe work besides the counter: the promotion kernels convert on the same half-rate integer pipe
-// that a heavier polling loop would occupy.  Returns true once the phase has completed.
-GI8_DEVICE bool mbar_poll(uint64_t* bar, uint32_t parity, uint32_t tries)
-{
-    uint32_t ok;
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p, q;\n\t"
-        ".reg .u32 n;\n\t"
-        "mov.u32 n, %3;\n\t"
-        "POLL:\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "@p bra.uni DONE;\n\t"
-        "sub.u32 n, n, 1;\n\t"
-        "setp.ne.u32 q, n, 0;\n\t"
-        "@q bra.uni POLL;\n\t"
-        "DONE:\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t"
-        "}\n"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity), "r"(tries)
-        : "memory");
-    return ok != 0;
-}
-
-constexpr uint32_t kWaitHintNs = 20000;  // per try_wait; the overall limit below is enforced with %globaltimer
 
 // Wall-clock limit of one wait.  Generous against any legitimate stall (a whole kernel takes
 // milliseconds), short enough that a protocol bug ends the kernel instead of hanging the GPU.
@@ -345,17 +296,6 @@ GI8_DEVICE void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 
-// tcgen05.st: registers -> TMEM, same addressing as the loads.  The source registers are read asynchronously:
-// they must keep their value until tmem_st_wait().
-GI8_DEVICE void tmem_st_32x32b_x8(uint32_t taddr, const uint32_t (&r)[8])
-{
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"r"(taddr), "r"(r[0]),
-                 "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
-
-GI8_DEVICE void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-
 GI8_DEVICE void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
 {
     asm volatile(
@@ -367,13 +307,6 @@ GI8_DEVICE void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[16])
         : "memory");
 }
 
-GI8_DEVICE void tmem_ld_32x32b_x8(uint32_t taddr, uint32_t (&r)[8])
-{
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
-}
 
 GI8_DEVICE void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -388,15 +321,6 @@ GI8_DEVICE uint32_t pack_bf16x2(float lo, float hi)
     return r;
 }
 
-// 16-byte streaming load: read-only path, no L1 allocation (the data is used once).
-GI8_DEVICE uint4 ld_nc_na(const uint4* p)
-{
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-                 : "l"(p));
-    return v;
-}
 
 GI8_DEVICE uint16_t to_bf16_bits(float f)
 {
@@ -436,12 +360,6 @@ GI8_DEVICE void st_dsmem_u32(uint32_t cluster_addr, uint32_t v)
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
-GI8_DEVICE int32_t ld_dsmem_s32(uint32_t cluster_addr)
-{
-    int32_t v;
-    asm volatile("ld.shared::cluster.s32 %0, [%1];" : "=r"(v) : "r"(cluster_addr) : "memory");
-    return v;
-}
 
 GI8_DEVICE void tma_load_2d_pair(void* smem_dst, const CUtensorMap* map, uint32_t leader_bar_cluster_addr, int32_t c0,
                                  int32_t c1)
