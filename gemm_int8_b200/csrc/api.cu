@@ -57,9 +57,15 @@ std::atomic<int> g_forced_variant{VAR_AUTO};
 //   GEMM_INT8_TMA_STORE  = 0       bf16 epilogues store from registers instead of through shared memory + TMA
 //   GEMM_INT8_PDL        = 0       small-M kernels are launched without programmatic dependent launch
 //   GEMM_INT8_SPLITS     = n       small-M kernels: number of K splits
-//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256, or (default) two column halves with N = 128
+//   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256, or two column halves with N = 128 (default:
+//                                  N = 256 for the one-CTA tile, column halves for the two-CTA tile)
 //   GEMM_INT8_BW_ISSUERS = 1 | 2   blockwise kernel without column halves: MMA-issuing threads (default: one for the
 //                                  256-wide tile, two for the narrower ones, whose MMAs are issue bound)
+//   GEMM_INT8_TAIL_SPLIT = 0 | 1 | 2   dense kernels: never / when the cost model says so (default) / whenever possible hand
+//                                  the last wave of the tile grid (or a thin grid) to the split-K kernel
+// and one promise by the host rather than a knob:
+//   GEMM_INT8_STATIC_WEIGHTS = 1   the weight operand of the small-M path is not written by the work that directly
+//                                  precedes the call in its stream: its first tiles may be requested early
 struct Knobs {
     int group_m = 0;
     bool tma_store = true;

@@ -188,8 +188,8 @@ GI8_DEVICE uint32_t pack_bf16x2_of(uint64_t pair)
 // PAIR: two CTAs on neighbouring SMs (a 2 x 1 x 1 cluster) share one 256 x BN tile, as in the dense kernel: the
 // leader's issuers run tcgen05.mma.cta_group::2 (M = 256), each CTA loads its own 128 rows of x and HALF of the BN
 // rows of y, keeps the partials of its 128 rows in its own tensor memory and promotes them with its own eight warps.
-// Per SM that is a third fewer operand bytes per K block (32 KB instead of 48 KB, so six pipeline stages instead of
-// four fit) and half the MMA instructions.  It matters because the 1-CTA kernel is bound by bytes in flight: with four
+// Per SM that is a third fewer operand bytes per K block (32 KB instead of 48 KB; four stages are used, six would fit
+// and measured the same) and half the MMA instructions.  It matters because the 1-CTA kernel is bound by bytes in flight: with four
 // 48 KB stages, one of them being read by the tensor core, 144 KB are in flight against an L2 latency of about 2000
 // cycles under load -- 72 bytes per cycle, i.e. 670 cycles per 48 KB K block where the tensor core needs 512.  TMA
 // loads are unicast into the issuing CTA's shared memory and signal the leader's barrier; the commits are two
