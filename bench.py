@@ -758,8 +758,10 @@ def main():
             "roofline": roofline,
             "cpu_baseline": cb,
             "e2e": e2e,
-            # one GEMM kernel of this library per step; two where the dense dispatch adds a split-K launch for the last wave
-            "gpu_launches": args.steps * (2 if "+splitk" in g.pick_variant({"blockwise": 2, "scaled": 1}.get(kind, 0), M, n_local, K) else 1),
+            # one GEMM kernel of this library per step; two where the dispatch adds a second launch for a thin last wave
+            # (dense: split-K kernel; blockwise: the remaining columns with narrower tiles)
+            "gpu_launches": args.steps * (2 if any(t in g.pick_variant({"blockwise": 2, "scaled": 1}.get(kind, 0), M, n_local, K)
+                                                   for t in ("+splitk", "+columns")) and not sharded else 1),
             "clocks": clock_summary,
             "kernel_status": status,
             "sweep": sweep,

@@ -296,6 +296,49 @@ int pick_group_m(int64_t K)
     return static_cast<int>(g);
 }
 
+// A blockwise tile cannot split K (the accumulation order is part of the result), so a grid of W full waves plus a few
+// tiles would pay W + 1 waves.  Where the full waves are whole column bands (W x SMs divisible by the row-block count),
+// the columns are split instead: the first launch covers the columns of the W full waves with 128 x 256 tiles, a second
+// launch covers the rest with the widest narrower tile that fits one wave -- more CTAs, each costing less per K block
+// (cycles of kBlockwiseForms).  The second launch reads nothing the first writes, so it is released as the first one's
+// CTAs leave (programmatic dependent launch without a wait before its work; it waits before it ends, see
+// BlockwiseParams::pdl_role).  kColumnSplitFixedCycles: set-up and epilogue of the second kernel's CTAs.  Measured on
+// B200, L2-cold: 512 x 10240 x 8192 (160 tiles) 75.8 -> 66.6 us, 512 x 57344 x 8192 256 -> 243, 2048 x 10240 x 8192 204 -> 196.
+constexpr double kColumnSplitFixedCycles = 10000.0;  // measured: a lone 64-wide launch of 64 K blocks takes 5 us more than its K blocks
+struct ColumnSplit {
+    bool use;
+    int64_t n1;   // columns of the first launch (a multiple of 256)
+    int bn_tail;  // tile width of the second launch
+};
+
+ColumnSplit plan_column_split(int64_t M, int64_t N, int64_t K, int sms)
+{
+    ColumnSplit c{};
+    if (knobs().tail_split == 0) return c;
+    const int64_t tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + 255) / 256;
+    const int64_t tiles = tiles_m * tiles_n;
+    const int64_t W = tiles / sms, rest = tiles - W * sms;
+    if (W == 0 || rest == 0 || (W * sms) % tiles_m != 0) return c;
+    const int64_t n1 = (W * sms / tiles_m) * 256;
+    const int64_t nt = N - n1;
+    if (n1 <= 0 || nt <= 0) return c;
+    const int kb = static_cast<int>((K + kBK - 1) / kBK);
+    double best = 1e300;
+    for (int i = 0; i < 4; ++i) {
+        const TileForm& f = kBlockwiseForms[i];
+        if (f.pair || f.bn == 256) continue;
+        if (tiles_m * ((nt + f.bn - 1) / f.bn) > sms) continue;  // one wave
+        if (f.kblock_cycles < best) best = f.kblock_cycles, c.bn_tail = f.bn;
+    }
+    if (c.bn_tail == 0) return c;
+    const double form = kBlockwiseForms[1].kblock_cycles + 16.0;
+    const double now = static_cast<double>(W + 1) * form * kb;
+    const double split = (static_cast<double>(W) * form + best + 16.0) * kb + kColumnSplitFixedCycles;
+    if (knobs().tail_split == 1 && split >= 0.98 * now) return c;
+    c.use = true, c.n1 = n1;
+    return c;
+}
+
 template <typename Kernel>
 int ensure_smem(DeviceState* st, int slot, Kernel kernel, size_t bytes)
 {
@@ -760,6 +803,10 @@ const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K)
     if (kind == 2) {
         bool pair = false;
         const int bn = pick_bn(M, N, sms, true, &pair);
+        if (bn == 256 && !pair && N % 8 == 0) {
+            const ColumnSplit c = plan_column_split(M, N, K, sms);
+            if (c.use) return c.bn_tail == 128 ? "blockwise_bn256+columns_bn128" : "blockwise_bn256+columns_bn64";
+        }
         return pair ? "blockwise_pair" : bn == 256 ? "blockwise_bn256" : bn == 128 ? "blockwise_bn128" : "blockwise_bn64";
     }
     const DenseChoice c = choose_dense(M, N, K, sms);
@@ -1048,7 +1095,7 @@ int gi8_quantize_token(const void* in, int in_dtype, int8_t* q, float* scales, i
 // peer's, the latter through mapped peer memory) instead of `out`.
 static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw, int64_t ld_sw,
                           void* out, int64_t M, int64_t N, int64_t K, void* stream, void* const* gather, int n_out,
-                          int64_t n_total, int64_t col0, bool out_f32 = false)
+                          int64_t n_total, int64_t col0, bool out_f32 = false, int force_bn = 0, int pdl_role = 0)
 {
     if (gather) out = gather[0];
     if (int rc = check_common(x, y, out, M, N, K, out_f32 ? 4 : 2)) return rc;
@@ -1085,6 +1132,8 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         case VAR_PAIR: bn = 256, pair = true; break;
         default: bn = pick_bn(M, N, st->sm_count, true, &pair);
     }
+    if (force_bn) bn = force_bn, pair = false;
+    p.pdl_role = pdl_role;
     // The epilogue's TMA-store boxes are 64 columns wide for the 256- and 128-wide tiles and 32 for the 64-wide one.
     // A box is clipped at the edge of the tensor map, i.e. of the whole [M, n_total] matrix, not at the edge of this
     // GEMM's column slice: a slice that starts or ends inside a box (and is not the last one) would overwrite its
@@ -1123,13 +1172,15 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         cfg.blockDim = dim3(kBlockwiseThreads, 1, 1);                                         \
         cfg.dynamicSmemBytes = smem;                                                          \
         cfg.stream = s;                                                                       \
-        cudaLaunchAttribute attr[1];                                                          \
+        cudaLaunchAttribute attr[2];                                                          \
         attr[0].id = cudaLaunchAttributeClusterDimension;                                     \
         attr[0].val.clusterDim.x = PAIR_ ? 2 : 1;                                             \
         attr[0].val.clusterDim.y = 1;                                                         \
         attr[0].val.clusterDim.z = 1;                                                         \
+        attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;                      \
+        attr[1].val.programmaticStreamSerializationAllowed = 1;                               \
         cfg.attrs = attr;                                                                     \
-        cfg.numAttrs = 1;                                                                     \
+        cfg.numAttrs = pdl_role == 2 ? 2 : 1;                                                 \
         GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mx, my, mo, p));                            \
     } while (0)
     const bool two = knobs().bw_issuers == 2 || (knobs().bw_issuers == 0 && bn < 256);
@@ -1156,6 +1207,22 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
 int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
                          int64_t ld_sw, void* out, int64_t M, int64_t N, int64_t K, void* stream)
 {
+    if (g_forced_variant == VAR_AUTO && M > 0 && N > 0 && K > 0 && out && reinterpret_cast<uintptr_t>(out) % 16 == 0 && N % 8 == 0) {
+        DeviceState* st;
+        if (int rc = get_device_state(&st)) return rc;
+        bool pair = false;
+        if (pick_bn(M, N, st->sm_count, true, &pair) == 256 && !pair) {
+            const ColumnSplit c = plan_column_split(M, N, K, st->sm_count);
+            if (c.use) {
+                // both launches write through a tensor map of the whole [M, N] matrix, each its own columns
+                void* outs[1] = {out};
+                if (int rc = blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, nullptr, M, c.n1, K, stream, outs, 1, N, 0, false, 256, 1))
+                    return rc;
+                return blockwise_impl(x, y + c.n1 * K, sa, ld_sa, sw ? sw + (c.n1 / 128) * ld_sw : sw, ld_sw, nullptr, M, N - c.n1, K,
+                                      stream, outs, 1, N, c.n1, false, c.bn_tail, 2);
+            }
+        }
+    }
     return blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, out, M, N, K, stream, nullptr, 1, N, 0);
 }
 

@@ -78,6 +78,10 @@ struct BlockwiseParams {
                     // N-sharded group: each rank's full [M, N_total] matrix, peers through mapped peer memory)
     int out_col0;   // column of this GEMM's first output column in those matrices
     int scale_vec;  // ceil(K/128) % 4 == 0 and the rows of sa and sw are 16-byte aligned: scales are loaded four at a time
+    int pdl_role;   // 0: none.  1: this launch is followed by an independent launch over other output columns: let it start
+                    // as SMs free up (griddepcontrol.launch_dependents).  2: that second launch: it reads nothing the first
+                    // one writes and therefore does not wait before working, but it waits for the first before it ends,
+                    // so that the completion of the pair means the completion of both.
     int out_f32;    // store the fp32 accumulators themselves (out is float [M,N]) instead of their bf16 cast; the
                     // partial results of a K-sharded GEMM, and the bit-exact check of the accumulation order
 };
@@ -252,6 +256,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
+        if (p.pdl_role == 1) pdl_launch_dependents();
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&bar_full[s], 1);
@@ -697,6 +702,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         if constexpr (PAIR) tmem_dealloc_pair(tmem_base, kTmemCols);
         else tmem_dealloc(tmem_base, kTmemCols);
     }
+    if (p.pdl_role == 2 && threadIdx.x == 0) pdl_wait();  // this grid ends only after the launch before it has ended
 }
 
 }  // namespace gi8

@@ -194,7 +194,8 @@ int gi8_hadamard_quantize_token_block(const void* in, int in_dtype, int8_t* q, f
 int gi8_force_variant(const char* name);
 
 /* Name of the variant the dispatch would pick for (kind, M, N, K); kind: 0 plain, 1 scaled, 2 blockwise (whose names
- * read "blockwise_bn256", "blockwise_bn128", "blockwise_bn64", "blockwise_pair").  For the dense kernels "+splitkS"
+ * read "blockwise_bn256", "blockwise_bn128", "blockwise_bn64", "blockwise_pair", and "blockwise_bn256+columns_bnW" where
+ * the columns of the thin last wave go to a second launch with W-wide tiles).  For the dense kernels "+splitkS"
  * after a form's name means that the tiles of its last wave go to the split-K kernel with S splits, and "splitkS" alone
  * that the whole grid does. */
 const char* gi8_pick_variant(int kind, int64_t M, int64_t N, int64_t K);

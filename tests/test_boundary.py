@@ -51,6 +51,8 @@ def test_dispatch_table_choices_without_gpu():
     assert pv(2, 2048, 11008, 4096) == "blockwise_bn256"
     assert pv(2, 16384, 57344, 8192) == "blockwise_pair"          # config 5: 193 waves
     assert pv(2, 128, 8192, 8192) == "blockwise_bn64"
+    assert pv(2, 512, 10240, 8192) == "blockwise_bn256+columns_bn64"   # 160 tiles: one full wave + the last 768 columns narrow
+    assert pv(2, 8192, 8192, 8192) == "blockwise_bn256"
     assert pv(1, 16, 4096, 4096) == "smallm_cluster" and pv(1, 64, 14336, 4096) == "smallm_cluster"
     assert pv(1, 2048, 4096, 4096) == "pair"                      # the scaled entry point above M = 64 is the dense kernel
 

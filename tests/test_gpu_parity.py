@@ -349,6 +349,37 @@ def test_blockwise_mma_forms_agree(g, oracle, halves, issuers, bw_knobs):
     g.force_variant(None)
 
 
+def test_blockwise_column_split_second_launch(g, oracle, monkeypatch):
+    """A blockwise grid of W full waves plus a few tiles is run as two launches over disjoint column ranges (the second with
+    narrower tiles, released as the first one's CTAs leave).  Forced wherever possible: the bits must stay the oracle's,
+    also for a ragged last tile, for back-to-back calls, and for a kernel that reads the result right behind the pair
+    (it must see both launches' columns)."""
+    monkeypatch.setenv("GEMM_INT8_TAIL_SPLIT", "2")
+    g.reload_env()
+    try:
+        gen = torch.Generator().manual_seed(77)
+        for (M, N, K) in [(512, 10240, 512), (512, 10232, 640), (256, 38400, 384)]:
+            assert "+columns_bn" in g.pick_variant(2, M, N, K), (M, N, K)
+            KB, NB = -(-K // 128), -(-N // 128)
+            x, y = rand_i8((M, K), M + 5), rand_i8((N, K), N + 5)
+            sa = torch.rand(M, KB, generator=gen) * 0.02 + 1e-3
+            sw = torch.rand(NB, KB, generator=gen) * 0.02 + 1e-3
+            ref = oracle.c_matmul_blockwise(x, y, sa, sw)
+            xd, yd, sad, swd = x.cuda(), y.cuda(), sa.cuda(), sw.cuda()
+            copies = []
+            for _ in range(3):
+                out = g.matmul_blockwise(xd, yd, sad, swd)
+                copies.append(out.clone())          # a kernel right behind the pair, on the same stream
+            for c in copies:
+                assert_bits_equal(oracle, c, ref, f"column split {(M, N, K)}")
+        assert g.device_status() == 0
+    finally:
+        monkeypatch.delenv("GEMM_INT8_TAIL_SPLIT", raising=False)
+        g.reload_env()
+    assert g.pick_variant(2, 512, 10240, 8192) == "blockwise_bn256+columns_bn64"
+    assert g.pick_variant(2, 8192, 8192, 8192) == "blockwise_bn256"
+
+
 def test_blockwise_unit_scales_are_exact_integers(g, oracle):
     """All scales 1 and |sums| < 2^24: the blockwise kernel must return bf16 of the exact int32 product, and
     single-K-block slices expose each int32 partial exactly."""
