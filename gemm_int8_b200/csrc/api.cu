@@ -442,13 +442,15 @@ int launch_dense_splitk(DeviceState* st, int slot, const int8_t* x, const int8_t
     cfg.blockDim = dim3(kDenseThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = q.splits;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = q.after_main ? 2 : 1;
     GI8_CUDA(cudaLaunchKernelEx(&cfg, kernel, mx, my, p, q));
     return GI8_OK;
 }
@@ -460,12 +462,15 @@ int launch_dense_splitk(DeviceState* st, int slot, const int8_t* x, const int8_t
 //   (waves - 1) x form + kb / S x 655 + fixed < what would run instead.
 // The fixed part was fitted on B200 (L2-cold runs): 16000 cycles when the split-K launch is the only one (its ramp-up
 // on cold operands, two cluster barriers, 128 KB of partials per CTA through distributed shared memory, stores of 8
-// bytes per thread), 26000 when it follows a main launch (a second, dependent launch on top).  With these numbers a
-// thin last wave moves only when one wave is long (K of about 8192 and more), and a thin grid when K is long against
-// its tile count (256 x 4096 x 28672: 62 -> 41 us; 512 x 4096 x 14336 and 128 x 8192 x 8192: level, left alone).
+// bytes per thread), 20000 when it follows a main launch.  The split-K launch reads nothing the main launch writes:
+// it is released by programmatic dependent launch as the main launch's CTAs leave, does not wait before its work, and
+// waits for the main grid before it ends (a fully dependent second launch had measured 26000).  With these numbers a
+// thin last wave moves only when one wave is long (1024 x 14336 x K: level at K = 4096, 90 -> 82 us at 8192, 167 -> 143
+// at 16384), and a thin grid when K is long against its tile count (256 x 4096 x 28672: 62 -> 41 us; 512 x 4096 x 14336
+// and 128 x 8192 x 8192: level, left alone).  A split must promise at least 1 % of the whole run.
 constexpr double kSplitKBlockCycles = 655.0;   // one-CTA 128 x 256 tile
 constexpr double kTailFixedAlone = 16000.0;
-constexpr double kTailFixedAfterMain = 26000.0;
+constexpr double kTailFixedAfterMain = 20000.0;
 struct TailPlan {
     bool use;
     int tile_end;  // tiles left to the main launch
@@ -494,7 +499,7 @@ TailPlan plan_tail(int64_t M, int64_t N, int64_t K, bool pair, double form_cycle
     const int kbs = (kb + S - 1) / S;
     const double now = now_per_kb >= 0.0 ? now_per_kb * kb : static_cast<double>(waves) * kb * (form_cycles + 16.0);
     const double split = static_cast<double>(waves - 1) * kb * (form_cycles + 16.0) + kbs * kSplitKBlockCycles + (waves > 1 ? kTailFixedAfterMain : kTailFixedAlone);
-    if (knobs().tail_split == 1 && split >= now) return t;
+    if (knobs().tail_split == 1 && split >= 0.99 * now) return t;
     t.use = true;
     t.tile_end = static_cast<int>((waves - 1) * slots);
     t.q.tile_begin = t.tile_end;
@@ -551,6 +556,8 @@ int dispatch_dense(DeviceState* st, const int8_t* x, const int8_t* y, DenseParam
         if (t.use && p.vec_ok) {
             DenseParams pm = p;
             pm.tile_end = t.tile_end;
+            pm.pdl_role = 1;
+            t.q.after_main = t.tile_end > 0 ? 1 : 0;
             DenseParams pt = p;  // the grid description the split-K kernel numbers its tiles by
             pt.tiles_m = static_cast<int>((p.M + (pair ? 2 * kBM : kBM) - 1) / (pair ? 2 * kBM : kBM));
             pt.tiles_n = static_cast<int>((p.N + 255) / 256);

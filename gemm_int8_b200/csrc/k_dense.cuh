@@ -50,6 +50,7 @@ struct DenseParams {
     int group_m;          // row-blocks per rasterisation band
     int tma_store;        // bf16 epilogues: stage 32 x 32 blocks in shared memory and write them with TMA stores
     int tile_end;         // > 0: only tiles [0, tile_end) of the grid are computed here (the rest by the split-K launch)
+    int pdl_role;         // 1: an independent launch over other output tiles follows: let it start as SMs free up
     float alpha;
 };
 
@@ -139,6 +140,7 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     const int tile_step = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
     if (threadIdx.x == 0) {
+        if (p.pdl_role == 1) pdl_launch_dependents();
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) {
             mbar_init(&bar_full[s], 1);

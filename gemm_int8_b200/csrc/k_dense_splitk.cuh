@@ -31,6 +31,8 @@ struct SplitKParams {
     int splits;         // S
     int kb_per_split;   // K blocks per split (the last may get fewer, or none)
     int pair_grid;      // the numbering is that of 256-row (two-CTA) tiles: unit u is half u % 2 of tile u / 2
+    int after_main;     // launched (with programmatic dependent launch) behind the main launch of the same GEMM: it
+                        // reads nothing that launch writes and starts as SMs free up, but ends only after it
 };
 
 GI8_DEVICE void st_dsmem_v4(uint32_t cluster_addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d)
@@ -77,7 +79,10 @@ dense_splitk_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (q.pair_grid) mb = 2 * mb + (unit & 1);
     }
     // The lower half of a 256-row tile can lie wholly below M: the whole cluster leaves (same decision in every CTA).
-    if (mb * kBM >= p.M) return;
+    if (mb * kBM >= p.M) {
+        if (q.after_main && threadIdx.x == 0) pdl_wait();
+        return;
+    }
 
     const int num_kb_total = (p.K + kBK - 1) / kBK;
     const int kb_begin = static_cast<int>(rank) * q.kb_per_split;
@@ -240,6 +245,7 @@ dense_splitk_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tcgen05_fence_after_sync();
         tmem_dealloc(tmem_base, kTmemCols);
     }
+    if (q.after_main && threadIdx.x == 0) pdl_wait();  // the pair of launches completes as one
 }
 
 }  // namespace gi8
