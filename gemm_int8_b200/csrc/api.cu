@@ -55,7 +55,7 @@ std::atomic<int> g_forced_variant{VAR_AUTO};
 // path calls getenv.
 //   GEMM_INT8_GROUP_M    = 1..64   row-blocks per rasterisation band (default: fitted to K)
 //   GEMM_INT8_TMA_STORE  = 0       bf16 epilogues store from registers instead of through shared memory + TMA
-//   GEMM_INT8_PDL        = 0       small-M kernels are launched without programmatic dependent launch
+//   GEMM_INT8_PDL        = 0       no programmatic dependent launch anywhere (small-M kernels, second launches of a GEMM)
 //   GEMM_INT8_SPLITS     = n       small-M kernels: number of K splits
 //   GEMM_INT8_BW_HALVES  = 1 | 2   blockwise 256-wide tile: MMAs with N = 256, or two column halves with N = 128 (default:
 //                                  N = 256 for the one-CTA tile, column halves for the two-CTA tile)
@@ -556,8 +556,9 @@ int dispatch_dense(DeviceState* st, const int8_t* x, const int8_t* y, DenseParam
         if (t.use && p.vec_ok) {
             DenseParams pm = p;
             pm.tile_end = t.tile_end;
-            pm.pdl_role = 1;
-            t.q.after_main = t.tile_end > 0 ? 1 : 0;
+            // (GEMM_INT8_PDL=0: the split-K launch is an ordinary, fully dependent second launch)
+            pm.pdl_role = knobs().pdl ? 1 : 0;
+            t.q.after_main = (t.tile_end > 0 && knobs().pdl) ? 1 : 0;
             DenseParams pt = p;  // the grid description the split-K kernel numbers its tiles by
             pt.tiles_m = static_cast<int>((p.M + (pair ? 2 * kBM : kBM) - 1) / (pair ? 2 * kBM : kBM));
             pt.tiles_n = static_cast<int>((p.N + 255) / 256);
@@ -1223,10 +1224,11 @@ int gi8_matmul_blockwise(const int8_t* x, const int8_t* y, const float* sa, int6
             if (c.use) {
                 // both launches write through a tensor map of the whole [M, N] matrix, each its own columns
                 void* outs[1] = {out};
-                if (int rc = blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, nullptr, M, c.n1, K, stream, outs, 1, N, 0, false, 256, 1))
+                const bool pdl = knobs().pdl;  // GEMM_INT8_PDL=0: two ordinary launches, one after the other
+                if (int rc = blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, nullptr, M, c.n1, K, stream, outs, 1, N, 0, false, 256, pdl ? 1 : 0))
                     return rc;
                 return blockwise_impl(x, y + c.n1 * K, sa, ld_sa, sw ? sw + (c.n1 / 128) * ld_sw : sw, ld_sw, nullptr, M, N - c.n1, K,
-                                      stream, outs, 1, N, c.n1, false, c.bn_tail, 2);
+                                      stream, outs, 1, N, c.n1, false, c.bn_tail, pdl ? 2 : 0);
             }
         }
     }

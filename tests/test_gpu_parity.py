@@ -177,8 +177,15 @@ def test_dense_split_k_tail(g, oracle, variant, monkeypatch):
                 x[0], y[0] = -128, -128   # the largest possible sums
             xd, yd = x.cuda(), y.cuda()
             for alpha in (1.0, -3.7):
-                out = g.matmul(xd, yd, alpha)
-                assert_bits_equal(oracle, out, oracle.c_matmul(x, y, alpha), f"split-K plain {variant} {(M, N, K)} alpha {alpha}")
+                ref = oracle.c_matmul(x, y, alpha)
+                for pdl in ("1", "0"):   # split-K launch released as the main launch's CTAs leave / an ordinary second launch
+                    monkeypatch.setenv("GEMM_INT8_PDL", pdl)
+                    g.reload_env()
+                    outs = [g.matmul(xd, yd, alpha).clone() for _ in range(2)]   # back to back, a reader right behind each
+                    for out in outs:
+                        assert_bits_equal(oracle, out, ref, f"split-K plain {variant} {(M, N, K)} alpha {alpha} pdl {pdl}")
+                monkeypatch.delenv("GEMM_INT8_PDL", raising=False)
+                g.reload_env()
             if M > 64:   # (smaller M goes to the small-M kernel)
                 sx = torch.rand(M, generator=gen) * 0.05 + 1e-3
                 sw = torch.rand(N, generator=gen) * 0.05 + 1e-3
@@ -366,12 +373,16 @@ def test_blockwise_column_split_second_launch(g, oracle, monkeypatch):
             sw = torch.rand(NB, KB, generator=gen) * 0.02 + 1e-3
             ref = oracle.c_matmul_blockwise(x, y, sa, sw)
             xd, yd, sad, swd = x.cuda(), y.cuda(), sa.cuda(), sw.cuda()
-            copies = []
-            for _ in range(3):
-                out = g.matmul_blockwise(xd, yd, sad, swd)
-                copies.append(out.clone())          # a kernel right behind the pair, on the same stream
-            for c in copies:
-                assert_bits_equal(oracle, c, ref, f"column split {(M, N, K)}")
+            for pdl in ("1", "0"):   # second launch released as the first one's CTAs leave / an ordinary second launch
+                monkeypatch.setenv("GEMM_INT8_PDL", pdl)
+                g.reload_env()
+                copies = []
+                for _ in range(3):
+                    out = g.matmul_blockwise(xd, yd, sad, swd)
+                    copies.append(out.clone())          # a kernel right behind the pair, on the same stream
+                for c in copies:
+                    assert_bits_equal(oracle, c, ref, f"column split {(M, N, K)} pdl {pdl}")
+            monkeypatch.delenv("GEMM_INT8_PDL", raising=False)
         assert g.device_status() == 0
     finally:
         monkeypatch.delenv("GEMM_INT8_TAIL_SPLIT", raising=False)
