@@ -34,6 +34,7 @@ SYMBOLS = {
     "gi8_matmul_scaled_static": (_i, [_p, _p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "gi8_matmul_blockwise": (_i, [_p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p]),
     "gi8_matmul_blockwise_f32": (_i, [_p, _p, _p, _i64, _p, _i64, _p, _i64, _i64, _i64, _p]),
+    "gi8_matmul_blockwise_f32_scatter": (_i, [_p, _p, _p, _i64, _p, _i64, _p, _i, _i, _i64, _i64, _i64, _p]),
     "gi8_sum_parts_bf16": (_i, [_p, _i, _i64, _p, _i64, _p]),
     "gi8_matmul_blockwise_allgather": (_i, [_p, _p, _p, _i64, _p, _i64, _p, _i, _i64, _i64, _i64, _i64, _i64, _p]),
     "gi8_peer_alloc": (_i, [_p, _i64]),

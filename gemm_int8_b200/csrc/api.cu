@@ -161,7 +161,7 @@ int get_device_state(DeviceState** out)
 struct MapKey {
     const void* base;
     uint64_t d0, d1, stride_bytes;
-    uint32_t box0, box1, kind;  // kind: 0 = int8 operand, 1 = bf16 output
+    uint32_t box0, box1, kind;  // kind: 0 = int8 operand, 1 = bf16 output, 2 = fp32 output
     bool operator==(const MapKey& o) const
     {
         return base == o.base && d0 == o.d0 && d1 == o.d1 && stride_bytes == o.stride_bytes && box0 == o.box0 &&
@@ -196,6 +196,10 @@ int cached_map(CUtensorMap* out, const MapKey& key)
     if (key.kind == 0)
         r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(key.base), dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    else if (key.kind == 2)
+        r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(key.base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     else
         r = g_encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(key.base), dims, strides, box, estr,
@@ -1103,8 +1107,11 @@ int gi8_quantize_token(const void* in, int in_dtype, int8_t* q, float* scales, i
 // peer's, the latter through mapped peer memory) instead of `out`.
 static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw, int64_t ld_sw,
                           void* out, int64_t M, int64_t N, int64_t K, void* stream, void* const* gather, int n_out,
-                          int64_t n_total, int64_t col0, bool out_f32 = false, int force_bn = 0, int pdl_role = 0)
+                          int64_t n_total, int64_t col0, bool out_f32 = false, int force_bn = 0, int pdl_role = 0,
+                          int scatter_me = -1)
 {
+    // scatter_me >= 0: `gather` holds the n_out ranks' receive areas of the K-sharded reduce-scatter form
+    const bool scatter = scatter_me >= 0;
     if (gather) out = gather[0];
     if (int rc = check_common(x, y, out, M, N, K, out_f32 ? 4 : 2)) return rc;
     if (M == 0 || N == 0) return GI8_OK;
@@ -1141,13 +1148,14 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
         default: bn = pick_bn(M, N, st->sm_count, true, &pair);
     }
     if (force_bn) bn = force_bn, pair = false;
+    if (scatter && bn == 64) bn = 128;  // a 32 x 32 fp32 box needs the 4 KB staging block of the wider tiles
     p.pdl_role = pdl_role;
     // The epilogue's TMA-store boxes are 64 columns wide for the 256- and 128-wide tiles and 32 for the 64-wide one.
     // A box is clipped at the edge of the tensor map, i.e. of the whole [M, n_total] matrix, not at the edge of this
     // GEMM's column slice: a slice that starts or ends inside a box (and is not the last one) would overwrite its
     // neighbour's columns, so such slices take the narrow tile, whose boxes the slice contract (multiples of 32)
     // always fits.
-    if (gather && (col0 % 64 != 0 || (N % 64 != 0 && col0 + N != n_total))) bn = 64, pair = false;
+    if (gather && !scatter && (col0 % 64 != 0 || (N % 64 != 0 && col0 + N != n_total))) bn = 64, pair = false;
     const int box_cols = blockwise_store_cols(bn);
     CUtensorMap mx, my;
     if (int rc = make_operand_map(&mx, x, M, K, kBM)) return rc;
@@ -1161,7 +1169,16 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
     const int slots = pair ? st->sm_count / 2 : st->sm_count;
     const int grid = static_cast<int>(tiles < slots ? tiles : slots) * (pair ? 2 : 1);
     OutputMaps mo{};
-    if (gather) {
+    if (scatter) {
+        // one fp32 map per rank over its receive area [n_out * R, N], boxes of 32 rows x 32 columns
+        const int64_t R = M / n_out;
+        for (int i = 0; i < n_out; ++i) {
+            MapKey key{gather[i], static_cast<uint64_t>(N), static_cast<uint64_t>(n_out * R), static_cast<uint64_t>(N) * 4, 32u, 32u, 2u};
+            if (int rc = cached_map(&mo.m[i], key)) return rc;
+        }
+        p.scatter_ranks = n_out, p.scatter_rows = static_cast<int>(R), p.scatter_me = scatter_me;
+        p.tma_store = 0, p.n_out = n_out;
+    } else if (gather) {
         for (int i = 0; i < n_out; ++i)
             if (int rc = make_output_map(&mo.m[i], gather[i], M, n_total, n_total, box_cols)) return rc;
         p.tma_store = 1, p.n_out = n_out, p.out_col0 = static_cast<int>(col0);
@@ -1282,6 +1299,21 @@ int gi8_matmul_blockwise_allgather(const int8_t* x, const int8_t* y, const float
                     (long long)(col0 + N), (long long)n_total);
     if (M > 0 && N > 0 && K == 0) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "K must be positive for the gathering form");
     return blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, nullptr, M, N, K, stream, outs, n_outs, n_total, col0);
+}
+
+int gi8_matmul_blockwise_f32_scatter(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                                     int64_t ld_sw, void* const* recv, int n_ranks, int my_rank, int64_t M, int64_t N,
+                                     int64_t K, void* stream)
+{
+    if (!recv || n_ranks < 1 || n_ranks > kMaxOutputs || my_rank < 0 || my_rank >= n_ranks)
+        return fail(GI8_ERR_INVALID_ARGUMENT, "n_ranks must be in [1, %d] and my_rank below it", kMaxOutputs);
+    for (int i = 0; i < n_ranks; ++i)
+        if (!recv[i] || reinterpret_cast<uintptr_t>(recv[i]) % 16)
+            return fail(GI8_ERR_MISALIGNED, "receive area %d is null or not 16-byte aligned", i);
+    if (M <= 0 || N <= 0 || K <= 0 || M % n_ranks || (M / n_ranks) % 32 || N % 4)
+        return fail(GI8_ERR_UNSUPPORTED_SHAPE, "the scattering form needs M a multiple of 32 x n_ranks (M=%lld, n_ranks=%d), "
+                    "N a multiple of 4 and K > 0", (long long)M, n_ranks);
+    return blockwise_impl(x, y, sa, ld_sa, sw, ld_sw, nullptr, M, N, K, stream, recv, n_ranks, N, 0, true, 0, 0, my_rank);
 }
 
 // Peer buffers for the gathering form: plain cudaMalloc allocations (an IPC handle names a whole allocation) and the

@@ -82,6 +82,9 @@ struct BlockwiseParams {
                     // as SMs free up (griddepcontrol.launch_dependents).  2: that second launch: it reads nothing the first
                     // one writes and therefore does not wait before working, but it waits for the first before it ends,
                     // so that the completion of the pair means the completion of both.
+    int scatter_ranks;  // > 0: K-sharded reduce-scatter form.  The fp32 accumulators of tile rows [j R, (j + 1) R), R =
+    int scatter_rows;   // scatter_rows, go to output matrix j (rank j's receive area, float [ranks, R, N], mapped peer
+    int scatter_me;     // memory for j != me) at row block scatter_me, as 32 x 32 fp32 TMA-store boxes; R % 32 == 0
     int out_f32;    // store the fp32 accumulators themselves (out is float [M,N]) instead of their bf16 cast; the
                     // partial results of a K-sharded GEMM, and the bit-exact check of the accumulation order
 };
@@ -599,7 +602,42 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             }
             if (!ok) break;
 
-            if (p.tma_store) {
+            if (p.scatter_ranks > 0) {
+                // fp32 accumulators, 32 rows x 32 columns per box (128-byte rows, 128-byte swizzle: the same staging
+                // block as a 32 x 64 bf16 box), to the output matrix of the rank that owns these rows.
+                int tile_again = tile, mb2, nb2;
+                asm volatile("" : "+r"(tile_again));
+                tile_coords(tile_again, p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
+                const int row0 = mb2 * kTileM + static_cast<int>(rank) * kBM + quarter * 32;
+                if (row0 < p.M) {
+                    const int owner = row0 / p.scatter_rows;   // warp-uniform; a 32-row block has one owner (R % 32 == 0)
+                    const int dst_row0 = p.scatter_me * p.scatter_rows + (row0 - owner * p.scatter_rows);
+                    const uint32_t stg = ((smem_u32(smem_raw) + 1023u) & ~1023u) + STAGES * kStageBytes + (warp - 4) * kStoreBytes;
+#pragma unroll
+                    for (int b = 0; b < CW / 32; ++b) {
+                        const int col0 = nb2 * BN + cg * kSegStrideCg + (b / (SEGW / 32)) * kSegStrideH + (b % (SEGW / 32)) * 32;
+                        if (col0 >= p.N) continue;  // warp-uniform
+                        if (lane == 0) tma_store_wait_read<0>();
+                        __syncwarp();
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            const int cq = q ^ (lane & 7);
+                            const int a0 = b * 16 + 2 * q;
+                            asm volatile("st.shared.v2.b64 [%0], {%1, %2};" ::"r"(stg + lane * 128 + cq * 16), "l"(acc[a0]), "l"(acc[a0 + 1])
+                                         : "memory");
+                        }
+                        fence_proxy_async_smem();
+                        __syncwarp();
+                        if (lane == 0) {
+                            asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                                             reinterpret_cast<uint64_t>(&outs.m[owner])),
+                                         "r"(stg), "r"(col0), "r"(dst_row0)
+                                         : "memory");
+                            tma_store_commit();
+                        }
+                    }
+                }
+            } else if (p.tma_store) {
                 // Blocks of 32 rows x STORE_W columns through swizzled shared memory and TMA stores (rows >= M and
                 // columns beyond the tensor map are clipped by the hardware).  The tile's coordinates are derived
                 // again from an opaque copy of the tile index so that they do not occupy registers across the

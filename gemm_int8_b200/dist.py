@@ -251,13 +251,113 @@ class FusedGatherGemm:
         self._own = []
 
 
-def _tensor_from_ptr(ptr: int, shape, device: torch.device) -> torch.Tensor:
-    """A bf16 tensor over device memory the library allocated (kept alive by its owner, not by the tensor)."""
+class FusedReduceScatterGemm:
+    """K-sharded (row-parallel) blockwise GEMM whose epilogue stores the fp32 accumulators of every row block straight
+    into the receive area of the rank that owns those rows (TMA stores through mapped peer memory), followed by a
+    barrier and the ordered sum + cast (`sum_parts_bf16`): the data movement of the reduce-scatter rides on the GEMM
+    tile by tile, and the result is bit-identical to `matmul_blockwise_ksharded` (same chains, same order of the sum).
+
+    Set-up (once per output shape): every rank allocates TWO receive areas, float ``[world, M / world, N]``, with the
+    library's peer allocator; CUDA IPC handles are exchanged through `torch.distributed`.  Calls alternate between the
+    two areas, which closes the cross-rank write-after-read window exactly as in `FusedGatherGemm` (consume the
+    result of call i before calling `run` for the second time after it; the barrier must be stream-ordered, i.e. NCCL,
+    otherwise `run` synchronises the stream first).  M must be a multiple of 32 * world, N of 4; at most 8 ranks.
+    """
+
+    def __init__(self, M: int, N: int, group=None):
+        import ctypes
+
+        import torch.distributed as dist
+
+        from . import _C, _lib
+
+        self._C, self._lib, self._ct = _C, _lib, ctypes
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("FusedReduceScatterGemm supports at most 8 ranks")
+        if M % (32 * self.world) or N % 4:
+            raise ValueError("M must be a multiple of 32 x world size and N a multiple of 4")
+        self.M, self.N, self.rows = M, N, M // self.world
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._stream_ordered = dist.get_backend(group) == "nccl"
+        nbytes = self.world * self.rows * N * 4
+        self._own, self._mapped, self._recv, self._views = [], [], [], []
+        for _ in range(2):
+            own = ctypes.c_void_p()
+            _lib.check(_C, _C.gi8_peer_alloc(ctypes.byref(own), nbytes))
+            self._own.append(own)
+            handle = (ctypes.c_ubyte * 64)()
+            _lib.check(_C, _C.gi8_peer_export(own, handle))
+            handles = [None] * self.world
+            dist.all_gather_object(handles, bytes(handle), group=group)
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(own.value)
+                    continue
+                buf = (ctypes.c_ubyte * 64).from_buffer_copy(h)
+                p = ctypes.c_void_p()
+                _lib.check(_C, _C.gi8_peer_import(buf, ctypes.byref(p)))
+                self._mapped.append(p)
+                ptrs.append(p.value)
+            self._recv.append((ctypes.c_void_p * self.world)(*ptrs))   # indexed by owning rank
+            self._views.append(_tensor_from_ptr(own.value, (self.world, self.rows, N), self.device, torch.float32))
+        self._turn = 0
+        dist.barrier(group=group)  # every rank has mapped every area before anyone writes
+
+    def run(self, x_q_shard: torch.Tensor, w_q_shard: torch.Tensor, x_scale_shard: torch.Tensor,
+            w_scale_shard: torch.Tensor) -> torch.Tensor:
+        """One kernel launch on the current stream, the cross-rank barrier, the ordered sum: returns this rank's bf16
+        ``[M / world, N]`` rows."""
+        import torch.distributed as dist
+
+        from . import sum_parts_bf16
+
+        M, _ = x_q_shard.shape
+        N = w_q_shard.shape[0]
+        if M != self.M or N != self.N:
+            raise ValueError("operand shapes do not match the receive areas")
+        turn = self._turn
+        self._turn ^= 1
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        rc = self._C.gi8_matmul_blockwise_f32_scatter(
+            x_q_shard.data_ptr(), w_q_shard.data_ptr(), x_scale_shard.data_ptr(), x_scale_shard.stride(0),
+            w_scale_shard.data_ptr(), w_scale_shard.stride(0), self._recv[turn], self.world, self.rank, M, N,
+            x_q_shard.shape[1], stream)
+        self._lib.check(self._C, rc)
+        if not self._stream_ordered:
+            torch.cuda.current_stream(self.device).synchronize()  # a host-only barrier orders nothing on the GPU
+        dist.barrier(group=self.group)
+        return sum_parts_bf16(self._views[turn])
+
+    def close(self) -> None:
+        """Unmaps the peers' areas and frees this rank's (collective: every rank must call it)."""
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=self.group)
+        for p in self._mapped:
+            self._lib.check(self._C, self._C.gi8_peer_release(p))
+        self._mapped = []
+        self._views = []
+        dist.barrier(group=self.group)  # nobody frees while a peer still has the area mapped
+        for own in self._own:
+            self._lib.check(self._C, self._C.gi8_peer_free(own))
+        self._own = []
+
+
+def _tensor_from_ptr(ptr: int, shape, device: torch.device, dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """A bf16 (or fp32) tensor over device memory the library allocated (kept alive by its owner, not by the tensor)."""
     n = 1
     for d in shape:
         n *= d
+    typestr, raw = ("<i2", torch.int16) if dtype == torch.bfloat16 else ("<i4", torch.int32)
 
     class _Mem:
-        __cuda_array_interface__ = {"shape": (n,), "typestr": "<i2", "data": (ptr, False), "version": 3}
+        __cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3}
 
-    return torch.as_tensor(_Mem(), device=device).view(torch.bfloat16).view(*shape)
+    t = torch.as_tensor(_Mem(), device=device)
+    assert t.dtype == raw
+    return t.view(dtype).view(*shape)

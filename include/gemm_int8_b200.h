@@ -122,6 +122,19 @@ int gi8_matmul_blockwise_f32(const int8_t* x, const int8_t* y, const float* sa, 
                              int64_t ld_sw, float* out_f32, int64_t M, int64_t N, int64_t K, void* stream);
 
 /*
+ * K-sharded (row-parallel) form with the reduce-scatter's data movement fused into the epilogue (no reference
+ * counterpart; the reference is single-GPU): this rank holds a K slice of x, y and both scale arrays, computes the fp32
+ * accumulators of the whole [M, N] output over its slice, and stores rows [j R, (j + 1) R), R = M / n_ranks, straight
+ * into recv[j] + my_rank * R * N -- recv[j] being rank j's receive area, float [n_ranks, R, N], the caller's own
+ * memory for j == my_rank and mapped peer memory otherwise (gi8_peer_*).  Only unicast TMA stores cross the links.
+ * After a barrier across the ranks each rank calls gi8_sum_parts_bf16 over its receive area.  Needs M a multiple of
+ * 32 * n_ranks, N a multiple of 4, n_ranks <= 8.
+ */
+int gi8_matmul_blockwise_f32_scatter(const int8_t* x, const int8_t* y, const float* sa, int64_t ld_sa, const float* sw,
+                                     int64_t ld_sw, void* const* recv, int n_ranks, int my_rank, int64_t M, int64_t N,
+                                     int64_t K, void* stream);
+
+/*
  * out[i] = bf16( ((parts[0][i] + parts[1][i]) + parts[2][i]) + ... ) for i < count, parts[r] = parts + r * part_stride:
  * the second step of a K-sharded GEMM -- the ranks' fp32 partials of one output slice, summed in the order given
  * (so the result does not depend on which rank finished first) and cast once.  No reference counterpart.

@@ -452,6 +452,53 @@ def test_blockwise_f32_accumulators_and_ksharded_sum(g, oracle):
     assert_bits_equal(oracle, g.sum_parts_bf16(odd), ref, "k-sharded, odd width")
 
 
+def test_blockwise_f32_scatter_entry_on_one_gpu(g, oracle):
+    """The reduce-scatter form through the C ABI with every rank's receive area on this GPU: rank r's launch must put
+    rows [j R, (j + 1) R) of its fp32 accumulators into area j at part r (and nothing anywhere else: the areas start
+    as NaN patterns and must be completely overwritten by the `world` launches), and the ordered sum of each area
+    must equal the oracle's K-sharded restatement.  All tile forms, ragged N, 2 and 4 ranks."""
+    from gemm_int8_b200 import dist as gdist
+
+    gen = torch.Generator().manual_seed(54)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    for variant in (None, "dense_bn256", "dense_bn128", "dense_bn64", "pair"):
+        g.force_variant(variant)
+        for (world, M, N, K) in [(2, 128, 520, 1024), (4, 384, 1000, 2048 + 128)]:
+            KB, NB = K // 128, -(-N // 128)
+            x, y = rand_i8((M, K), M + 9), rand_i8((N, K), N + 9)
+            sa = torch.rand(M, KB, generator=gen) * 0.02 + 1e-3
+            sw = torch.rand(NB, KB, generator=gen) * 0.02 + 1e-3
+            R = M // world
+            areas = [torch.full((world, R, N), float("nan"), dtype=torch.float32, device="cuda") for _ in range(world)]
+            recv = (ctypes.c_void_p * world)(*[a.data_ptr() for a in areas])
+            keep = []
+            for r in range(world):
+                k0, k1 = gdist.kshard_bounds(K, world, r)
+                ops = (x[:, k0:k1].contiguous().cuda(), y[:, k0:k1].contiguous().cuda(),
+                       sa[:, k0 // 128:k1 // 128].contiguous().cuda(), sw[:, k0 // 128:k1 // 128].contiguous().cuda())
+                keep.append(ops)
+                rc = g._C.gi8_matmul_blockwise_f32_scatter(
+                    ctypes.c_void_p(ops[0].data_ptr()), ctypes.c_void_p(ops[1].data_ptr()), ctypes.c_void_p(ops[2].data_ptr()),
+                    ops[2].stride(0), ctypes.c_void_p(ops[3].data_ptr()), ops[3].stride(0), recv, world, r, M, N, k1 - k0, stream)
+                assert rc == 0, g._C.gi8_last_error()
+            ref = oracle.c_matmul_blockwise_ksharded(x, y, sa, sw, world)
+            for j in range(world):
+                assert not torch.isnan(areas[j]).any(), f"area {j} not fully written ({variant}, world {world})"
+                out = g.sum_parts_bf16(areas[j])
+                assert_bits_equal(oracle, out, ref[j * R:(j + 1) * R], f"scatter {variant} world {world} rows of rank {j}")
+    g.force_variant(None)
+    # argument checks
+    a = torch.zeros((2, 32, 64), dtype=torch.float32, device="cuda")
+    recv = (ctypes.c_void_p * 2)(a.data_ptr(), a.data_ptr())
+    xq = torch.zeros((64, 128), dtype=torch.int8, device="cuda")
+    sc = torch.ones((64, 1), dtype=torch.float32, device="cuda")
+    args = (ctypes.c_void_p(xq.data_ptr()), ctypes.c_void_p(xq.data_ptr()), ctypes.c_void_p(sc.data_ptr()), 1,
+            ctypes.c_void_p(sc.data_ptr()), 1)
+    assert g._C.gi8_matmul_blockwise_f32_scatter(*args, recv, 2, 2, 64, 64, 128, stream) == 1    # my_rank out of range
+    assert g._C.gi8_matmul_blockwise_f32_scatter(*args, recv, 2, 0, 48, 64, 128, stream) == 2    # M not a multiple of 32 x ranks
+    assert g._C.gi8_matmul_blockwise_f32_scatter(*args, recv, 9, 0, 288, 64, 128, stream) == 1   # more than 8 ranks
+
+
 def test_config2_blockwise_prefill_full_size(g, oracle):
     from gemm_int8_b200 import workloads
 
