@@ -1177,6 +1177,8 @@ static int blockwise_impl(const int8_t* x, const int8_t* y, const float* sa, int
             if (int rc = cached_map(&mo.m[i], key)) return rc;
         }
         p.scatter_ranks = n_out, p.scatter_rows = static_cast<int>(R), p.scatter_me = scatter_me;
+        // rank r starts with (about) its own rows: tiles are numbered band by band over the row blocks
+        p.tile_rot = static_cast<int>(tiles * scatter_me / n_out);
         p.tma_store = 0, p.n_out = n_out;
     } else if (gather) {
         for (int i = 0; i < n_out; ++i)

@@ -85,6 +85,8 @@ struct BlockwiseParams {
     int scatter_ranks;  // > 0: K-sharded reduce-scatter form.  The fp32 accumulators of tile rows [j R, (j + 1) R), R =
     int scatter_rows;   // scatter_rows, go to output matrix j (rank j's receive area, float [ranks, R, N], mapped peer
     int scatter_me;     // memory for j != me) at row block scatter_me, as 32 x 32 fp32 TMA-store boxes; R % 32 == 0
+    int tile_rot;       // the tile sequence starts at this tile (and wraps): in the scattering form rank r starts with its
+                        // own rows, so that at any moment the ranks send to different owners instead of all to the same
     int out_f32;    // store the fp32 accumulators themselves (out is float [M,N]) instead of their bf16 cast; the
                     // partial results of a K-sharded GEMM, and the bit-exact check of the accumulation order
 };
@@ -178,6 +180,13 @@ GI8_DEVICE uint32_t pack_bf16x2_of(uint64_t pair)
     float lo, hi;
     unpack_f32x2(pair, lo, hi);
     return pack_bf16x2(lo, hi);
+}
+
+// Position `tile` of the sequence that starts at tile `rot` and wraps at `n` (rot < n).
+GI8_DEVICE int rotate_tile(int tile, int rot, int n)
+{
+    const int t = tile + rot;
+    return t >= n ? t - n : t;
 }
 
 // Makes a 32-bit value opaque to the optimiser at this point, so that later uses read the register instead of
@@ -302,7 +311,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             bool ok = true;
             for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
                 int mb, nb;
-                tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
+                tile_coords(rotate_tile(tile, p.tile_rot, num_tiles), p.tiles_m, p.tiles_n, mb, nb, p.group_m);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     bool freed = wait_or_abort(&bar_done[0][s], ph ^ 1, &abort_flag);
                     if (SPLIT == 2 && freed) freed = wait_or_abort(&bar_done[SPLIT - 1][s], ph ^ 1, &abort_flag);
@@ -472,7 +481,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 
         for (int tile = first_tile; tile < num_tiles && ok; tile += tile_step) {
             int mb, nb;
-            tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m);
+            tile_coords(rotate_tile(tile, p.tile_rot, num_tiles), p.tiles_m, p.tiles_n, mb, nb, p.group_m);
             const int row = mb * kTileM + static_cast<int>(rank) * kBM + quarter * 32 + lane;
             const bool row_ok = row < p.M;
             // First output column of this warp's segment in half 0 (half h: kSegStrideH further).  A segment lies
@@ -607,7 +616,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 // block as a 32 x 64 bf16 box), to the output matrix of the rank that owns these rows.
                 int tile_again = tile, mb2, nb2;
                 asm volatile("" : "+r"(tile_again));
-                tile_coords(tile_again, p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
+                tile_coords(rotate_tile(tile_again, p.tile_rot, num_tiles), p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
                 const int row0 = mb2 * kTileM + static_cast<int>(rank) * kBM + quarter * 32;
                 if (row0 < p.M) {
                     const int owner = row0 / p.scatter_rows;   // warp-uniform; a 32-row block has one owner (R % 32 == 0)
@@ -644,7 +653,7 @@ blockwise_gemm_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                 // promotion loop.
                 int tile_again = tile, mb2, nb2;
                 asm volatile("" : "+r"(tile_again));
-                tile_coords(tile_again, p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
+                tile_coords(rotate_tile(tile_again, p.tile_rot, num_tiles), p.tiles_m, p.tiles_n, mb2, nb2, p.group_m);
                 const int row0 = mb2 * kTileM + static_cast<int>(rank) * kBM + quarter * 32;
                 if (row0 < p.M) {
                     const uint32_t stg = ((smem_u32(smem_raw) + 1023u) & ~1023u) + STAGES * kStageBytes + (warp - 4) * kStoreBytes;
