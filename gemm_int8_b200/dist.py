@@ -200,8 +200,9 @@ class FusedGatherGemm:
                 _lib.check(_C, _C.gi8_peer_import(buf, ctypes.byref(p)))
                 self._mapped.append(p)
                 ptrs.append(p.value)
-            # own matrix first (the entry point takes any order; outs[0] is only used for argument checks)
-            order = [self.rank] + [r for r in range(self.world) if r != self.rank]
+            # own matrix first, then the peers in cyclic order from this rank on (the entry point takes any order; the
+            # kernel stores every block to the matrices in this order, so at any moment the ranks address different peers)
+            order = [(self.rank + i) % self.world for i in range(self.world)]
             self._outs.append((ctypes.c_void_p * self.world)(*[ptrs[r] for r in order]))
             self._views.append(_tensor_from_ptr(own.value, (M, N), self.device))
         self._turn = 0
