@@ -1,10 +1,16 @@
-"""Column-wise (N) sharding of a large GEMM over the GPUs of one box, and the gather of the bf16 slices.
+"""Sharding of a large GEMM over the GPUs of one box: column-wise (N) with the gather of the bf16 slices, and
+K-wise (row-parallel layers) with the reduce-scatter of fp32 partials.
 
 The reference is single-GPU (no collective call sites anywhere in its tree).  Output columns of
 ``x @ y.T`` are independent, so rank r keeps rows ``[n0, n1)`` of the weight ``y`` (and the matching rows
 of the 128x128-block weight scales), every rank holds the full activation ``x``, and each computes its
 ``[M, n1 - n0]`` slice with the unchanged single-GPU kernel: no communication inside the GEMM.  Only when
-the caller needs the whole matrix are the slices exchanged, with one NCCL all-gather over NVLink.
+the caller needs the whole matrix are the slices exchanged: with one NCCL all-gather over NVLink
+(`all_gather_slices`), or by the GEMM kernel itself, whose epilogue stores every block into every rank's matrix
+through mapped peer memory (`FusedGatherGemm`).  With K sharded instead, every rank computes fp32 partial sums of
+the whole output over its K slice; row blocks are exchanged by one all-to-all (`matmul_blockwise_ksharded`) or
+stored by the GEMM epilogue straight into the owning rank's receive area (`FusedReduceScatterGemm`), and added in
+rank order.
 
 One process per GPU; ``torch.distributed`` must be initialised by the caller (backend "nccl" on GPUs;
 the index logic also runs under "gloo" on CPU tensors, which is how it is tested without GPUs).
