@@ -61,8 +61,9 @@ std::atomic<int> g_forced_variant{VAR_AUTO};
 //                                  N = 256 for the one-CTA tile, column halves for the two-CTA tile)
 //   GEMM_INT8_BW_ISSUERS = 1 | 2   blockwise kernel without column halves: MMA-issuing threads (default: one for the
 //                                  256-wide tile, two for the narrower ones, whose MMAs are issue bound)
-//   GEMM_INT8_TAIL_SPLIT = 0 | 1 | 2   dense kernels: never / when the cost model says so (default) / whenever possible hand
-//                                  the last wave of the tile grid (or a thin grid) to the split-K kernel
+//   GEMM_INT8_TAIL_SPLIT = 0 | 1 | 2   never / when the cost model says so (default) / whenever possible hand the last wave
+//                                  of a tile grid to a second launch: the split-K kernel (dense entry points; also a whole
+//                                  thin grid), narrower tiles over the remaining columns (blockwise entry point)
 // and one promise by the host rather than a knob:
 //   GEMM_INT8_STATIC_WEIGHTS = 1   the weight operand of the small-M path is not written by the work that directly
 //                                  precedes the call in its stream: its first tiles may be requested early

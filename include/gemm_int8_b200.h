@@ -237,8 +237,9 @@ int gi8_selftest_wait_timeout(void* stream);
 /*
  * The GEMM_INT8_* tuning variables (tile band height, TMA-store epilogue, programmatic dependent launch, K splits,
  * blockwise MMA shape and issuer count, GEMM_INT8_TAIL_SPLIT = 0 / 1 / 2: never / when the cost model says so / whenever
- * possible send a thin last wave of the dense kernels to the split-K kernel) are read once, when the library is first
- * used; this reads them again.
+ * possible give a thin last wave of a tile grid to a second launch -- the split-K kernel for the dense entry points,
+ * narrower tiles over the remaining columns for the blockwise one) are read once, when the library is first used; this
+ * reads them again.
  * GEMM_INT8_STATIC_WEIGHTS=1 (default 0) is a promise rather than a tuning: the weight operand of gi8_matmul_scaled's
  * small-M path is not written by the work that directly precedes the call in its stream (weights quantised ahead of
  * time), so the kernel may request its first weight tiles while that work is still finishing.  Activations, scales
