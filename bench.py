@@ -706,7 +706,10 @@ def main():
             s_.clear()
         torch.cuda.empty_cache()
         peaks_, _ = load_peaks()
-        sweep = run_sweep(torch, g, dev, flush_buf, peaks_)
+        try:
+            sweep = run_sweep(torch, g, dev, flush_buf, peaks_)
+        except Exception as exc:  # the main line must not be lost to the extra rows
+            sweep = [{"error": repr(exc)[:300]}]
         status = status or g.device_status()
 
     # N > 1: the K-sharded (row-parallel) form on the Llama-70B down-projection shape of config 4 (K = 28672 split over the
