@@ -1045,8 +1045,8 @@ int gi8_quantize_token_block(const void* in, int in_dtype, int8_t* q, float* sca
     if (int rc = get_device_state(&st)) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int KB = static_cast<int>((K + 127) / 128);
-    // A warp takes kQuantUnroll loads of 32 lanes x 16 bytes per iteration: 4 (fp32) or 8 (bf16) blocks.
-    const int64_t per_warp = (in_dtype == 0 ? 1 : 2) * kQuantUnroll;
+    // A warp takes eight 128-wide blocks per iteration: eight loads of 32 lanes x 16 bytes (fp32) or four (bf16).
+    const int64_t per_warp = kQuantBlocksPerItem;
     const int64_t warps = M * ((KB + per_warp - 1) / per_warp);  // one work item per warp and iteration
     if (warps >= (int64_t(1) << 32)) return fail(GI8_ERR_UNSUPPORTED_SHAPE, "too many quantisation blocks");
     int64_t blocks = (warps + kQuantThreads / 32 - 1) / (kQuantThreads / 32);

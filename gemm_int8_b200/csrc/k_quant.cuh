@@ -92,23 +92,26 @@ GI8_DEVICE void load4<__nv_bfloat16>(const __nv_bfloat16* p, bool ok, float (&v)
 // 16-byte loads: lane l of a group of LPB = 128 / EPL lanes owns EPL = 16 / sizeof(T) consecutive elements of one
 // 128-wide K block, a warp covers 32 / LPB blocks per load, and kQuantUnroll loads are issued before the first is
 // used so that enough bytes are in flight to cover the DRAM latency (one block per warp at a time reached a
-// quarter of the copy bandwidth).
+// quarter of the copy bandwidth; four loads per lane, held as fp32, 0.55 of it on bf16 input).  The loaded 16 bytes
+// stay in registers as they came (four registers per load whatever the type) and are unpacked at their use: a byte in
+// flight costs a register byte, and bf16 unpacked to fp32 before the wait had cost two.  fp32 input, which is bound by
+// the memory system, takes eight loads per lane (0.76-0.78 -> 0.84-0.86 of the copy bandwidth); bf16 input, which is bound
+// by instruction issue (about eighteen instructions per element), four (eight measured 3 % slower).
 // a [M,K] (K % EPL == 0, rows 16-byte aligned) -> q int8 [M,K], s fp32 [M, ceil(K/128)].
-constexpr int kQuantUnroll = 4;
+constexpr int kQuantBlocksPerItem = 8;  // 128-wide blocks per warp and iteration, whatever the type (1 x 8 or 2 x 4)
 
 template <typename T>
-GI8_DEVICE void load16(const T* p, bool ok, float (&v)[16 / sizeof(T)]);
+GI8_DEVICE void unpack16(const uint4& u, float (&v)[16 / sizeof(T)]);
 
 template <>
-GI8_DEVICE void load16<float>(const float* p, bool ok, float (&v)[4])
+GI8_DEVICE void unpack16<float>(const uint4& u, float (&v)[4])
 {
-    load4<float>(p, ok, v);
+    v[0] = __uint_as_float(u.x), v[1] = __uint_as_float(u.y), v[2] = __uint_as_float(u.z), v[3] = __uint_as_float(u.w);
 }
 
 template <>
-GI8_DEVICE void load16<__nv_bfloat16>(const __nv_bfloat16* p, bool ok, float (&v)[8])
+GI8_DEVICE void unpack16<__nv_bfloat16>(const uint4& u, float (&v)[8])
 {
-    uint4 u = ok ? __ldg(reinterpret_cast<const uint4*>(p)) : make_uint4(0u, 0u, 0u, 0u);
     v[0] = __uint_as_float(u.x << 16), v[1] = __uint_as_float(u.x & 0xffff0000u);
     v[2] = __uint_as_float(u.y << 16), v[3] = __uint_as_float(u.y & 0xffff0000u);
     v[4] = __uint_as_float(u.z << 16), v[5] = __uint_as_float(u.z & 0xffff0000u);
@@ -123,7 +126,9 @@ quantize_token_block_kernel(const T* __restrict__ a, int8_t* __restrict__ q, flo
     constexpr int EPL = 16 / sizeof(T);   // elements per lane and load
     constexpr int LPB = 128 / EPL;        // lanes per 128-wide block
     constexpr int BPL = 32 / LPB;         // blocks per warp and load
+    constexpr int kQuantUnroll = sizeof(T) == 4 ? 8 : 4;  // 16-byte loads per lane in flight
     constexpr int BPI = BPL * kQuantUnroll;  // blocks per warp and iteration
+    static_assert(BPI == kQuantBlocksPerItem, "the host sizes the grid by this");
     const int lane = threadIdx.x & 31;
     const int sub = lane / LPB, ll = lane % LPB;
     // Work item = BPI consecutive blocks of one row (one 32-bit division per item instead of one 64-bit division
@@ -133,35 +138,34 @@ quantize_token_block_kernel(const T* __restrict__ a, int8_t* __restrict__ q, flo
     const uint32_t items_total = static_cast<uint32_t>(M) * groups;  // the host checks that this fits
     for (uint32_t item = blockIdx.x * (kQuantThreads / 32) + (threadIdx.x >> 5); item < items_total; item += warps_total) {
         const uint32_t row = item / groups;
-        const int kb0 = static_cast<int>(item - row * groups) * BPI;
-        float v[kQuantUnroll][EPL];
-        int64_t off[kQuantUnroll];
-        bool ok[kQuantUnroll];
-        int kbs[kQuantUnroll];
+        const int kb0 = static_cast<int>(item - row * groups) * BPI + sub;   // this lane's block of load 0
+        const int col0 = kb0 * 128 + ll * EPL;                               // load u: BPL blocks further per u
+        const int64_t off0 = static_cast<int64_t>(row) * K + col0;
+        uint4 raw[kQuantUnroll];
 #pragma unroll
         for (int u = 0; u < kQuantUnroll; ++u) {
-            kbs[u] = kb0 + u * BPL + sub;
-            const int col = kbs[u] * 128 + ll * EPL;
-            ok[u] = col < K;   // also false for blocks past the end of the row
-            off[u] = static_cast<int64_t>(row) * K + col;
-            load16<T>(a + (ok[u] ? off[u] : 0), ok[u], v[u]);
+            const bool ok = col0 + u * (BPL * 128) < K;   // also false for blocks past the end of the row
+            raw[u] = ok ? __ldg(reinterpret_cast<const uint4*>(a + (off0 + u * (BPL * 128)))) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int u = 0; u < kQuantUnroll; ++u) {
+            float v[EPL];
+            unpack16<T>(raw[u], v);
             float amax = 0.0f;
 #pragma unroll
-            for (int j = 0; j < EPL; ++j) amax = fmaxf(amax, fabsf(v[u][j]));
+            for (int j = 0; j < EPL; ++j) amax = fmaxf(amax, fabsf(v[j]));
 #pragma unroll
             for (int o = LPB / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
             const QuantScale sc = make_quant_scale(amax);
-            if (ll == 0 && kbs[u] < KB) s[static_cast<int64_t>(row) * KB + kbs[u]] = sc.s;
-            if (ok[u]) {
+            const int kb = kb0 + u * BPL;
+            if (ll == 0 && kb < KB) s[static_cast<int64_t>(row) * KB + kb] = sc.s;
+            if (col0 + u * (BPL * 128) < K) {
                 uint32_t w[EPL / 4];
 #pragma unroll
-                for (int j = 0; j < EPL; j += 4)
-                    w[j / 4] = quant_pack4(v[u][j], v[u][j + 1], v[u][j + 2], v[u][j + 3], sc);
-                if constexpr (EPL == 8) *reinterpret_cast<uint2*>(q + off[u]) = make_uint2(w[0], w[1]);
-                else *reinterpret_cast<uint32_t*>(q + off[u]) = w[0];
+                for (int j = 0; j < EPL; j += 4) w[j / 4] = quant_pack4(v[j], v[j + 1], v[j + 2], v[j + 3], sc);
+                int8_t* dst = q + (off0 + u * (BPL * 128));
+                if constexpr (EPL == 8) *reinterpret_cast<uint2*>(dst) = make_uint2(w[0], w[1]);
+                else *reinterpret_cast<uint32_t*>(dst) = w[0];
             }
         }
     }
