@@ -642,11 +642,13 @@ def main():
     e2e = None
     if not args.no_e2e:
         host_in = [t.pin_memory() for t in inputs]
-        # Sharded: every rank copies its operands in; rank 0 reads the assembled matrix back (the other ranks' copies
-        # are identical), the others read back nothing.
-        reads_back = (not sharded) or rank == 0
+        # Sharded: every rank copies its operands in.  Fused gather: every rank holds the assembled [M, N] matrix and reads
+        # back its own block of M / world rows, so that the whole result reaches host memory exactly once, spread over
+        # the ranks' PCIe links.  NCCL gather (block layout [world, M, n_local]): rank 0 reads everything back.
+        rows_each = M // world if (sharded and fused is not None and M % world == 0) else 0
+        reads_back = (not sharded) or rank == 0 or rows_each > 0
         if sharded:
-            out_shape = (M, N) if fused is not None else (world, M, n_local)
+            out_shape = ((rows_each, N) if rows_each else (M, N)) if fused is not None else (world, M, n_local)
         else:
             out_shape = (M, n_local)
         host_out = torch.empty(out_shape if reads_back else (1,), dtype=torch.bfloat16).pin_memory()
@@ -669,7 +671,7 @@ def main():
             s = [t.to(dev, non_blocking=True) for t in host_in]
             out = op(s)
             if reads_back:
-                host_out.copy_(out, non_blocking=True)
+                host_out.copy_(out[rank * rows_each:(rank + 1) * rows_each] if rows_each else out, non_blocking=True)
 
         for _ in range(2):
             e2e_step()
@@ -696,8 +698,9 @@ def main():
         e2e = {"value": 2.0 * M * N * K * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TOPS",
                "h2d_bytes_per_step": int(tot[0].item()), "d2h_bytes_per_step": int(tot[1].item()), "steps": e2e_steps,
                "api": ("gemm_int8_b200.host.HostPipeline (2 calls in flight)" if pipe is not None else
-                       "gemm_int8_b200 ops + gather on one stream per rank; every rank copies its operands in, rank 0 "
-                       "copies the assembled matrix out")}
+                       "gemm_int8_b200 ops + gather on one stream per rank; every rank copies its operands in and " +
+                       ("its own M / world rows of the assembled matrix out (the whole result is read back once, spread "
+                        "over the ranks)" if rows_each else "rank 0 copies the assembled matrix out"))}
         del host_in, host_out
 
     sweep = None
